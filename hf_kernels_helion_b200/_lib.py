@@ -1,0 +1,58 @@
+"""ctypes binding of libb200fp8.so (C ABI: include/b200fp8.h).
+
+There is deliberately no fallback: if the shared library is missing or a call
+returns a non-zero status, a RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libb200fp8.so"
+
+OUT_BF16, OUT_FP32 = 0, 1
+VARIANT_AUTO, VARIANT_TILE128, VARIANT_TILE256, VARIANT_STREAMK = 0, 1, 2, 3
+VARIANT_NAMES = {"auto": 0, "tile128": 1, "tile256": 2, "streamk": 3}
+
+# name -> (restype, argtypes); mirrors include/b200fp8.h one to one
+SIGNATURES = {
+    "b200fp8_version": (c_int, []),
+    "b200fp8_strerror": (c_char_p, [c_int]),
+    "b200fp8_quant_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "b200fp8_quant_weight": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                     c_void_p]),
+    "b200fp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                             c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p,
+                             c_void_p]),
+    "b200fp8_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
+    "b200fp8_gemm_pick_variant": (c_int, [c_int64, c_int64, c_int64]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m hf_kernels_helion_b200.build` "
+                "(there is no non-CUDA fallback)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+def strerror(status: int) -> str:
+    return load().b200fp8_strerror(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise RuntimeError(f"{what} failed: b200fp8 status {status} ({strerror(status)})")

@@ -1,0 +1,346 @@
+// C ABI of the block-FP8 hot path (declarations and contracts: include/b200fp8.h).
+// Host side only validates, builds TMA descriptors and launches; nothing here
+// allocates, frees or synchronises.
+#include "../../include/b200fp8.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "gemm_streamk.cuh"
+#include "gemm_tile.cuh"
+#include "quant.cuh"
+
+namespace {
+
+using namespace b200fp8;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+  std::atomic<int> ready{0};
+  int cc_major = 0;
+  int sm_count = 0;
+};
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_mutex;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::atomic<EncodeTiledFn> g_encode{nullptr};
+
+// Per-device facts, read once; also opts every kernel into its dynamic shared memory size.
+int device_info(const DeviceInfo** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200FP8_ERR_ARCH;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!d.ready.load(std::memory_order_relaxed)) {
+      if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+          cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return B200FP8_ERR_ARCH;
+      if (d.cc_major != 10) return B200FP8_ERR_ARCH;
+      bool ok = true;
+      auto opt_in = [&ok](const void* fn, int bytes) {
+        ok = ok && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+      };
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128>), TileCfg<128>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256>), TileCfg<256>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<16>), StreamKCfg<16>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<32>), StreamKCfg<32>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<64>), StreamKCfg<64>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<128>), StreamKCfg<128>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<256>), StreamKCfg<256>::SMEM_BYTES);
+      if (!ok) {
+        cudaGetLastError();
+        return B200FP8_ERR_LAUNCH;
+      }
+      d.ready.store(1, std::memory_order_release);
+    }
+  }
+  *out = &d;
+  return B200FP8_OK;
+}
+
+int sm_count_or_default() {
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d) == B200FP8_OK) return d->sm_count;
+  cudaGetLastError();
+  return 148;  // B200
+}
+
+EncodeTiledFn encode_fn() {
+  EncodeTiledFn fn = g_encode.load(std::memory_order_acquire);
+  if (fn != nullptr) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  g_encode.store(fn, std::memory_order_release);
+  return fn;
+}
+
+// 2-D tensor map over a row-major byte matrix [rows, cols] with row stride ld (bytes),
+// box = [box_rows x 128 bytes], 128-byte swizzle, zero fill outside the matrix.
+int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200FP8_ERR_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  const cuuint32_t box[2] = {128u, box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200FP8_OK : B200FP8_ERR_DRIVER;
+}
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? B200FP8_OK : B200FP8_ERR_LAUNCH; }
+
+int streamk_mp(int64_t M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct StreamKPlan {
+  int mp;
+  int num_kb;
+  int64_t num_tiles;
+  int64_t grid;
+  int64_t ast_bytes;      // AsT region (first)
+  int64_t partial_bytes;  // partial-sum region (second)
+};
+
+StreamKPlan streamk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+  StreamKPlan p;
+  p.mp = streamk_mp(M);
+  p.num_kb = static_cast<int>((K + 127) / 128);
+  p.num_tiles = (N + 127) / 128;
+  const int64_t total = p.num_tiles * p.num_kb;
+  p.grid = total < sm_count ? total : sm_count;
+  if (p.grid < 1) p.grid = 1;
+  p.ast_bytes = align_up(static_cast<int64_t>(p.num_kb) * p.mp * 4, 256);
+  p.partial_bytes = 2 * p.grid * p.mp * 128 * 4;
+  return p;
+}
+
+double wave_efficiency(int64_t tiles, int sms) {
+  if (tiles <= 0) return 1.0;
+  const int64_t waves = (tiles + sms - 1) / sms;
+  return static_cast<double>(tiles) / static_cast<double>(waves * sms);
+}
+
+int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
+  (void)K;
+  if (M <= 256) return B200FP8_VARIANT_STREAMK;
+  const int64_t num_m = (M + 127) / 128;
+  const double e128 = wave_efficiency(num_m * ((N + 127) / 128), sm_count);
+  const double e256 = wave_efficiency(num_m * ((N + 255) / 256), sm_count);
+  // the 128x256 tile moves 25 % fewer operand bytes per flop; prefer it unless the last wave is much emptier
+  return (e256 * 1.15 >= e128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
+}
+
+template <int BN>
+int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb, int sm_count,
+                cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int st = make_tmap_u8(&ta, A, args.M, args.K, lda, 128);
+  if (st != B200FP8_OK) return st;
+  st = make_tmap_u8(&tb, B, args.N, args.K, ldb, BN);
+  if (st != B200FP8_OK) return st;
+  const int64_t tiles = ((args.M + 127) / 128) * ((args.N + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  gemm_tile_kernel<BN><<<grid, TileCfg<BN>::THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, args);
+  return launch_status();
+}
+
+template <int MP>
+int launch_streamk(const void* A, const void* B, const StreamKArgs& args, int64_t lda, int64_t ldb, int64_t grid,
+                   cudaStream_t stream) {
+  CUtensorMap tw, tx;
+  int st = make_tmap_u8(&tw, B, args.N, args.K, ldb, 128);
+  if (st != B200FP8_OK) return st;
+  st = make_tmap_u8(&tx, A, args.M, args.K, lda, MP);
+  if (st != B200FP8_OK) return st;
+  gemm_streamk_kernel<MP><<<static_cast<int>(grid), StreamKCfg<MP>::THREADS, StreamKCfg<MP>::SMEM_BYTES, stream>>>(
+      tw, tx, args);
+  return launch_status();
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200fp8_version(void) { return 100; }
+
+const char* b200fp8_strerror(int status) {
+  switch (status) {
+    case B200FP8_OK: return "ok";
+    case B200FP8_ERR_NULL: return "a required pointer is NULL";
+    case B200FP8_ERR_SHAPE: return "bad shape or leading dimension";
+    case B200FP8_ERR_ALIGN: return "pointer or leading dimension violates a 16-byte alignment rule";
+    case B200FP8_ERR_DTYPE: return "unknown output dtype";
+    case B200FP8_ERR_VARIANT: return "unknown kernel variant, or variant cannot run this shape";
+    case B200FP8_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200FP8_ERR_ARCH: return "current CUDA device is not compute capability 10.x (B200)";
+    case B200FP8_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or rejected the tensor";
+    case B200FP8_ERR_LAUNCH: return "CUDA runtime refused the kernel launch";
+    case B200FP8_ERR_TOO_LARGE: return "request exceeds a fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int b200fp8_quant_act(const void* x, void* q, float* s, int64_t M, int64_t K, int64_t ldx, int64_t ldq, int64_t lds,
+                      void* stream) {
+  if (M < 0 || K < 0) return B200FP8_ERR_SHAPE;
+  if (M == 0 || K == 0) return B200FP8_OK;
+  if (x == nullptr || q == nullptr || s == nullptr) return B200FP8_ERR_NULL;
+  if (ldx < K || ldq < K || lds < (K + 127) / 128) return B200FP8_ERR_SHAPE;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(q) & 7u) != 0)
+    return B200FP8_ERR_ALIGN;
+  const DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  const int64_t groups = M * ((K + 127) / 128);
+  const int64_t blocks_needed = (groups * 8 + 255) / 256;
+  const int64_t max_blocks = static_cast<int64_t>(dev->sm_count) * 32;
+  const int grid = static_cast<int>(blocks_needed < max_blocks ? blocks_needed : max_blocks);
+  quant_act_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), s, M, K, ldx, ldq, lds);
+  return launch_status();
+}
+
+int b200fp8_quant_weight(const void* w, void* q, float* s, int64_t N, int64_t K, int64_t ldw, int64_t ldq, int64_t lds,
+                         void* stream) {
+  if (N < 0 || K < 0) return B200FP8_ERR_SHAPE;
+  if (N == 0 || K == 0) return B200FP8_OK;
+  if (w == nullptr || q == nullptr || s == nullptr) return B200FP8_ERR_NULL;
+  if (ldw < K || ldq < K || lds < (K + 127) / 128) return B200FP8_ERR_SHAPE;
+  if (K % 8 != 0 || ldw % 8 != 0 || ldq % 8 != 0 || (reinterpret_cast<uintptr_t>(w) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(q) & 7u) != 0)
+    return B200FP8_ERR_ALIGN;
+  const DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  const int64_t blocks = ((N + 127) / 128) * ((K + 127) / 128);
+  if (blocks > 0x7FFFFFFF) return B200FP8_ERR_TOO_LARGE;
+  quant_weight_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), s, N, K, ldw, ldq, lds);
+  return launch_status();
+}
+
+int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) { return pick_variant(M, N, K, sm_count_or_default()); }
+
+int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
+  if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
+  const int sms = sm_count_or_default();
+  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return 0;
+  if (variant != B200FP8_VARIANT_STREAMK) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
+  if (M > 256) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
+  if (M == 0 || N == 0 || K == 0) return 0;
+  const StreamKPlan p = streamk_plan(M, N, K, sms);
+  return p.ast_bytes + p.partial_bytes;
+}
+
+int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M, int64_t N,
+                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc, int out_dtype,
+                 int variant, void* workspace, size_t workspace_bytes, uint32_t* status_word, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
+  if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
+  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_STREAMK) return B200FP8_ERR_VARIANT;
+  if (M == 0 || N == 0) return B200FP8_OK;
+  if (C == nullptr) return B200FP8_ERR_NULL;
+  if (ldc < N) return B200FP8_ERR_SHAPE;
+
+  const DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+
+  if (K == 0) {
+    gemm_zero_fill_kernel<<<dev->sm_count, 256, 0, stream>>>(C, M, N, ldc, out_dtype == B200FP8_OUT_FP32);
+    return launch_status();
+  }
+  if (A == nullptr || B == nullptr || As == nullptr || Bs == nullptr) return B200FP8_ERR_NULL;
+  const int64_t kblocks = (K + 127) / 128;
+  if (lda < K || ldb < K || ld_as < kblocks || ld_bs < kblocks) return B200FP8_ERR_SHAPE;
+  if (lda % 16 != 0 || ldb % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(B) & 15u) != 0)
+    return B200FP8_ERR_ALIGN;
+  if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
+
+  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
+
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) {
+    GemmArgs args;
+    args.As = As;
+    args.Bs = Bs;
+    args.C = C;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.ld_as = ld_as;
+    args.ld_bs = ld_bs;
+    args.ldc = ldc;
+    args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
+    args.status_word = status_word;
+    return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(A, B, args, lda, ldb, dev->sm_count, stream)
+                                              : launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream);
+  }
+
+  // stream-K decode variant
+  if (M > 256) return B200FP8_ERR_VARIANT;
+  const StreamKPlan p = streamk_plan(M, N, K, dev->sm_count);
+  if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < p.ast_bytes + p.partial_bytes)
+    return B200FP8_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
+  float* ast = static_cast<float*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + p.ast_bytes);
+
+  {
+    const int total = p.num_kb * p.mp;
+    streamk_prep_kernel<<<(total + 255) / 256, 256, 0, stream>>>(As, ast, M, p.num_kb, ld_as, p.mp);
+    st = launch_status();
+    if (st != B200FP8_OK) return st;
+  }
+  StreamKArgs args;
+  args.Bs = Bs;
+  args.AsT = ast;
+  args.partial = partial;
+  args.C = C;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ld_bs = ld_bs;
+  args.ldc = ldc;
+  args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
+  args.status_word = status_word;
+  switch (p.mp) {
+    case 16: st = launch_streamk<16>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 32: st = launch_streamk<32>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 64: st = launch_streamk<64>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 128: st = launch_streamk<128>(A, B, args, lda, ldb, p.grid, stream); break;
+    default: st = launch_streamk<256>(A, B, args, lda, ldb, p.grid, stream); break;
+  }
+  if (st != B200FP8_OK) return st;
+  streamk_fixup_kernel<<<static_cast<int>(p.num_tiles), 128, 0, stream>>>(
+      partial, C, M, N, p.num_kb, ldc, out_dtype == B200FP8_OUT_FP32, p.mp, p.grid);
+  return launch_status();
+}
+
+}  // extern "C"

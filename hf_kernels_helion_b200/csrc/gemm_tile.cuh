@@ -1,0 +1,291 @@
+// Persistent, warp-specialised block-FP8 GEMM for sm_100a:  C[M,N] = A[M,K] . B[N,K]^T
+// with fp32 scales As[M, K/128] (per token, per 128-wide K group) and
+// Bs[N/128, K/128] (per 128x128 weight block).
+//
+// Roles inside one CTA (one CTA per SM, tiles handed out round-robin):
+//   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per K block
+//               into a STAGES-deep shared-memory ring (SWIZZLE_128B, no multicast)
+//   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block into
+//               one of two TMEM accumulator stages, then tcgen05.commit to release the
+//               smem slot and to publish the TMEM stage
+//   warp 2      TMEM allocation / deallocation
+//   warps 4..   promotion + epilogue: tcgen05.ld the fp32 partial of one K block,
+//               acc += partial * (As[row, kb] * Bs[nb, kb]) in registers (the block
+//               scales are arbitrary fp32, so partial sums cannot stay in TMEM across
+//               K blocks), and after the last K block convert and store the tile.
+// The two TMEM stages let the MMA of K block k+1 overlap the promotion of block k.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace b200fp8 {
+
+struct GemmArgs {
+  const float* As;
+  const float* Bs;
+  void* C;
+  int64_t M, N, K;
+  int64_t ld_as, ld_bs, ldc;
+  int out_fp32;
+  uint32_t* status_word;
+};
+
+template <int BN_>
+struct TileCfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = BN_;
+  static constexpr int BK = 128;  // fp8 elements = bytes = one 128-byte swizzle span
+  static constexpr int STAGES = (BN_ == 128) ? 6 : 4;
+  static constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quarter
+  static constexpr int EPI_COLS = BN_ / 2;          // accumulator columns (registers) per epilogue thread
+  static constexpr int THREADS = 128 + 32 * EPI_WARPS;
+  // 128 accumulators + 64 staging registers per epilogue thread do not fit the 168
+  // registers a 384-thread CTA gets by default: the BN = 256 kernel moves registers
+  // from the producer/MMA warpgroup to the two epilogue warpgroups with setmaxnreg.
+  static constexpr bool REBALANCE_REGS = (BN_ == 256);
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN_ * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN_;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TileCfg<BN>::THREADS, 1)
+gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs args) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                  // [STAGES]  TMA bytes landed
+  uint64_t* empty = bars + STAGES;        // [STAGES]  MMA finished reading the slot
+  uint64_t* tfull = bars + 2 * STAGES;    // [2]       TMEM stage holds a finished K-block partial
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]    every epilogue warp has read the TMEM stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], Cfg::EPI_WARPS);
+    }
+    *abort_flag = 0u;
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int64_t M = args.M, N = args.N, K = args.K;
+  const int num_m = static_cast<int>((M + Cfg::BM - 1) / Cfg::BM);
+  const int num_n = static_cast<int>((N + BN - 1) / BN);
+  const int num_kb = static_cast<int>((K + Cfg::BK - 1) / Cfg::BK);
+  const int num_tiles = num_m * num_n;
+  uint32_t* status_word = args.status_word;
+
+  if (warp < 4) {
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<40>();
+  }
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % num_m) * Cfg::BM;
+        const int n0 = (tile / num_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status_word)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
+          tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+        }
+      }
+      if (!ok) {
+        // Abort path: let this CTA's own copies in flight land before shared memory is released.
+        const uint32_t first = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
+        for (uint32_t j = first; j < it; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1u)) {
+            if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_e4m3_f32(128, BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          const uint32_t ts = it & 1u;
+          const uint32_t tph = (it >> 1) & 1u;
+          if (!mbar_wait(&tempty[ts], tph ^ 1u, abort_flag, status_word)) { ok = false; break; }
+          if (!mbar_wait(&full[s], ph, abort_flag, status_word)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint64_t a_desc = make_smem_desc_sw128(a_addr);
+          const uint64_t b_desc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
+          const uint32_t d_tmem = tmem_base + ts * BN;
+#pragma unroll
+          for (int k = 0; k < Cfg::BK / 32; ++k) {
+            // +2 in the start-address field = +32 bytes = one K=32 slice of e4m3
+            umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+          tc_commit(&tfull[ts]);
+        }
+      }
+      if (!ok && it > 0) {
+        // Abort path: bounded wait for the MMAs already issued.
+        const uint32_t j = it - 1;
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&tfull[j & 1u], (j >> 1) & 1u)) {
+          if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ promotion + epilogue
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<232>();
+    const int e = warp - 4;
+    const int q = warp & 3;           // TMEM lane quarter this warp may read
+    const int cw = e >> 2;            // which 64-column slice of the tile
+    const int num_nb = static_cast<int>((N + 127) / 128);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % num_m) * Cfg::BM;
+      const int n0 = (tile / num_m) * BN;
+      const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
+      const int64_t row_c = row < M ? row : M - 1;
+      const int col0 = n0 + cw * Cfg::EPI_COLS;
+      int nb = col0 / 128;
+      nb = nb < num_nb ? nb : num_nb - 1;
+      const float* as_row = args.As + row_c * args.ld_as;
+      const float* bs_row = args.Bs + static_cast<int64_t>(nb) * args.ld_bs;
+
+      float acc[Cfg::EPI_COLS];
+#pragma unroll
+      for (int j = 0; j < Cfg::EPI_COLS; ++j) acc[j] = 0.f;
+
+      float sc_next = __ldg(as_row) * __ldg(bs_row);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const float sc = sc_next;
+        if (kb + 1 < num_kb) sc_next = __ldg(as_row + kb + 1) * __ldg(bs_row + kb + 1);
+        const uint32_t ts = it & 1u;
+        const uint32_t tph = (it >> 1) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ts * BN + cw * Cfg::EPI_COLS;
+#pragma unroll
+        for (int c = 0; c < Cfg::EPI_COLS; c += 64) {
+          uint32_t p0[32], p1[32];
+          tmem_ld_32x32(taddr + c, p0);
+          tmem_ld_32x32(taddr + c + 32, p1);
+          tmem_ld_wait();
+          if (c + 64 == Cfg::EPI_COLS) {
+            // the whole slice of this TMEM stage is in registers: hand the stage back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[ts]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(__uint_as_float(p0[j]), sc, acc[c + j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c + 32 + j] = fmaf(__uint_as_float(p1[j]), sc, acc[c + 32 + j]);
+        }
+      }
+      if (!ok) break;
+
+      if (row < M && col0 < N) {
+        if (args.out_fp32) {
+          float* crow = reinterpret_cast<float*>(args.C) + row * args.ldc + col0;
+          if (col0 + Cfg::EPI_COLS <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < Cfg::EPI_COLS; j += 4)
+              *reinterpret_cast<float4*>(crow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::EPI_COLS; ++j)
+              if (col0 + j < N) crow[j] = acc[j];
+          }
+        } else {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + row * args.ldc + col0;
+          if (col0 + Cfg::EPI_COLS <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < Cfg::EPI_COLS; j += 8) {
+              __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[j], acc[j + 1]);
+              __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[j + 2], acc[j + 3]);
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[j + 4], acc[j + 5]);
+              __nv_bfloat162 v3 = __floats2bfloat162_rn(acc[j + 6], acc[j + 7]);
+              uint4 u;
+              u.x = *reinterpret_cast<uint32_t*>(&v0);
+              u.y = *reinterpret_cast<uint32_t*>(&v1);
+              u.z = *reinterpret_cast<uint32_t*>(&v2);
+              u.w = *reinterpret_cast<uint32_t*>(&v3);
+              *reinterpret_cast<uint4*>(crow + j) = u;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::EPI_COLS; ++j)
+              if (col0 + j < N) crow[j] = __float2bfloat16_rn(acc[j]);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// C[M,N] = 0 for the degenerate K == 0 product.
+__global__ void gemm_zero_fill_kernel(void* C, int64_t M, int64_t N, int64_t ldc, int out_fp32) {
+  const int64_t total = M * N;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / N, c = i % N;
+    if (out_fp32)
+      reinterpret_cast<float*>(C)[r * ldc + c] = 0.f;
+    else
+      reinterpret_cast<__nv_bfloat16*>(C)[r * ldc + c] = __float2bfloat16_rn(0.f);
+  }
+}
+
+}  // namespace b200fp8

@@ -1,0 +1,104 @@
+"""Column-parallel (N-sharded) block-FP8 linear over the GPUs of one node.
+
+The reference has no multi-GPU code; this layer follows directly from its kernel's
+data dependence (torch-ext/finegrained_fp8_helion/fp8.py:30-36): an output column
+block ``C[:, n0:n1]`` reads only rows ``n0:n1`` of ``B`` and rows ``n0/128:n1/128`` of
+``Bs``, while ``A`` / ``As`` are used whole.  So rank r keeps the r-th slice of the
+weight's N rows, every rank computes its column slice of C with the single-GPU
+kernel, and ONE all-gather of the bf16 slices over NCCL / NVLink assembles [M, N].
+
+One process per GPU (torchrun); ``torch.distributed`` must be initialised.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(N: int, world: int, rank: int, block_n: int = 128):
+    """Rows [n0, n1) of the weight that `rank` owns.  N must split into `world` equal
+    slices that are whole 128-row scale blocks."""
+    if N % (world * block_n) != 0:
+        raise ValueError(f"N = {N} must be a multiple of world_size * {block_n} = {world * block_n}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weight(B: torch.Tensor, Bs: torch.Tensor, world: int, rank: int, block_n: int = 128):
+    """Slice a full block-FP8 weight ``B [N, K]`` / ``Bs [N/128, K/128]`` for `rank`."""
+    n0, n1 = shard_bounds(B.shape[0], world, rank, block_n)
+    return B[n0:n1], Bs[n0 // block_n:n1 // block_n]
+
+
+class ShardedFp8Linear:
+    """Holds this rank's weight slice and runs  C = A . B^T  tensor-parallel.
+
+    matmul: callable ``(A, B, As, Bs, block_size, output_dtype) -> [M, N_local]``;
+    defaults to the package's CUDA op.  (The CPU tests inject a checker here to
+    exercise the sharding and gather logic under gloo without a GPU.)
+    """
+
+    def __init__(self, B_local: torch.Tensor, Bs_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                 matmul: Optional[Callable] = None):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.B, self.Bs = B_local, Bs_local
+        self.n_local = B_local.shape[0]
+        if self.n_local % 128 != 0:
+            raise ValueError("the local weight slice must be a whole number of 128-row blocks")
+        self._injected = matmul is not None
+        self.matmul = matmul
+        self._gather_buf = None
+
+    @classmethod
+    def from_full(cls, B: torch.Tensor, Bs: torch.Tensor, group=None, matmul=None) -> "ShardedFp8Linear":
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        b, bs = shard_weight(B, Bs, world, rank)
+        return cls(b.contiguous(), bs.contiguous(), group, matmul)
+
+    @property
+    def N(self) -> int:
+        return self.n_local * self.world
+
+    def _buffer(self, M: int, dtype, device) -> torch.Tensor:
+        b = self._gather_buf
+        if b is None or b.shape[1] != M or b.dtype != dtype or b.device != device:
+            b = torch.empty((self.world, M, self.n_local), dtype=dtype, device=device)
+            self._gather_buf = b
+        return b
+
+    def local(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16, out=None) -> torch.Tensor:
+        """This rank's column slice C[:, n0:n1] (no communication), written into `out` if given."""
+        if self._injected:
+            res = self.matmul(A, self.B, As, self.Bs, [128, 128], output_dtype)
+            if out is None:
+                return res
+            out.copy_(res)
+            return out
+        from . import runtime  # noqa: PLC0415
+        return runtime.gemm(A, self.B, As, self.Bs, 128, 128, output_dtype, out=out)
+
+    def forward_slots(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
+        """Compute and all-gather; returns the gather buffer [world, M, N/world] whose slot r
+        is rank r's column slice.  ``slots.permute(1, 0, 2)`` is a zero-copy [M, world, N/world]
+        view holding the same values as C[M, N].  The GEMM writes straight into this rank's
+        slot and the all-gather runs in place, so the only extra traffic is the gather itself."""
+        buf = self._buffer(A.shape[0], output_dtype, A.device)
+        mine = buf[self.rank]
+        self.local(A, As, output_dtype, out=mine)
+        if self.world > 1:
+            dist.all_gather_into_tensor(buf.view(-1), mine.reshape(-1), group=self.group)
+        return buf
+
+    def forward(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
+        """Contiguous C [M, N] on every rank (all-gather, then one transpose copy of the slots)."""
+        slots = self.forward_slots(A, As, output_dtype)
+        M = A.shape[0]
+        return slots.permute(1, 0, 2).reshape(M, self.N)
+
+    __call__ = forward

@@ -1,0 +1,139 @@
+/*
+ * b200fp8 — C ABI of the B200 (sm_100a) block-FP8 hot path.
+ *
+ * The library replaces the device side of the reference package
+ * finegrained-fp8-helion (AmesingFlank/hf_kernels_helion):
+ *
+ *   finegrained-fp8-helion/finegrained-fp8-helion/torch-ext/finegrained_fp8_helion/fp8.py:19-39
+ *       the Helion kernel `_w8a8_block_fp8_matmul`            -> b200fp8_gemm
+ *   .../torch-ext/finegrained_fp8_helion/__init__.py:14
+ *       the separate `.to(output_dtype)` pass                 -> folded into b200fp8_gemm (out_dtype)
+ *   per-token-group activation quantiser (absent from the reference, defined by
+ *       the benchmark configuration text: scale = group amax / 448, e4m3 cast) -> b200fp8_quant_act
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name says host;
+ *   - leading dimensions (ld*) are in ELEMENTS of the tensor they belong to;
+ *   - no function allocates, frees or synchronises; kernels are enqueued on
+ *     `stream` (a cudaStream_t passed as void*, NULL = legacy default stream);
+ *   - every function returns a b200fp8_status (0 = ok) and never throws;
+ *   - `status_word` (may be NULL) is a device uint32 the kernels write a non-zero
+ *     code into when a bounded device-side wait gives up; the caller reads it
+ *     after synchronising the stream.
+ */
+#ifndef B200FP8_H_
+#define B200FP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200fp8_status {
+  B200FP8_OK = 0,
+  B200FP8_ERR_NULL = 1,       /* a required pointer is NULL */
+  B200FP8_ERR_SHAPE = 2,      /* M, N or K is negative, or a leading dimension is too small */
+  B200FP8_ERR_ALIGN = 3,      /* pointer or leading dimension breaks a 16-byte rule */
+  B200FP8_ERR_DTYPE = 4,      /* out_dtype is not one of B200FP8_OUT_* */
+  B200FP8_ERR_VARIANT = 5,    /* unknown variant, or variant cannot run this shape */
+  B200FP8_ERR_WORKSPACE = 6,  /* workspace missing or smaller than b200fp8_gemm_workspace_bytes */
+  B200FP8_ERR_ARCH = 7,       /* current device is not compute capability 10.x */
+  B200FP8_ERR_DRIVER = 8,     /* cuTensorMapEncodeTiled unavailable or rejected the tensor */
+  B200FP8_ERR_LAUNCH = 9,     /* the CUDA runtime refused the launch (see cudaGetLastError) */
+  B200FP8_ERR_TOO_LARGE = 10  /* request exceeds a fixed capacity of the entry point */
+} b200fp8_status;
+
+/* out_dtype of b200fp8_gemm */
+#define B200FP8_OUT_BF16 0
+#define B200FP8_OUT_FP32 1
+
+/* variant of b200fp8_gemm */
+#define B200FP8_VARIANT_AUTO 0    /* pick by shape */
+#define B200FP8_VARIANT_TILE128 1 /* persistent tcgen05 kernel, 128x128 output tiles */
+#define B200FP8_VARIANT_TILE256 2 /* persistent tcgen05 kernel, 128x256 output tiles */
+#define B200FP8_VARIANT_STREAMK 3 /* swap-AB stream-K kernel for M <= 256 (decode shapes), needs workspace */
+
+/* codes a kernel may leave in *status_word */
+#define B200FP8_DEV_OK 0u
+#define B200FP8_DEV_WAIT_TIMEOUT 1u /* an mbarrier wait exceeded its time limit; output is invalid */
+
+/* Library version, major*10000 + minor*100 + patch. */
+int b200fp8_version(void);
+
+/* Static English description of a status code. Never NULL. */
+const char* b200fp8_strerror(int status);
+
+/*
+ * Per-token-group activation quantiser (no counterpart function in the reference;
+ * it is the producer of the A / As arguments of
+ * torch-ext/finegrained_fp8_helion/__init__.py:7-11).
+ *
+ *   x  [M, K] bf16, row stride ldx          (read)
+ *   q  [M, K] float8_e4m3fn, row stride ldq (written)
+ *   s  [M, ceil(K/128)] fp32, row stride lds (written)
+ *
+ * For every row and every 128-wide group along K:
+ *   amax = max |x|, s = amax / 448 (fp32 IEEE division), q = e4m3_rne(x / s);
+ *   an all-zero group gives s = 0 and q = 0. A ragged last group (K % 128 != 0)
+ *   takes its amax over the elements that exist.
+ * Requires K % 8 == 0, ldx % 8 == 0, ldq % 8 == 0 and x, q 16- and 8-byte aligned.
+ */
+int b200fp8_quant_act(const void* x, void* q, float* s,
+                      int64_t M, int64_t K,
+                      int64_t ldx, int64_t ldq, int64_t lds,
+                      void* stream);
+
+/*
+ * 128x128-block weight quantiser (generator side of the path; no counterpart in
+ * the reference, whose callers receive B / Bs ready-made:
+ * torch-ext/finegrained_fp8_helion/__init__.py:9-11).
+ *
+ *   w  [N, K] bf16, row stride ldw            (read)
+ *   q  [N, K] float8_e4m3fn, row stride ldq   (written)
+ *   s  [ceil(N/128), ceil(K/128)] fp32, row stride lds (written)
+ * Same arithmetic as b200fp8_quant_act with the amax taken over a 128x128 block.
+ */
+int b200fp8_quant_weight(const void* w, void* q, float* s,
+                         int64_t N, int64_t K,
+                         int64_t ldw, int64_t ldq, int64_t lds,
+                         void* stream);
+
+/*
+ * Block-FP8 W8A8 GEMM, C = A . B^T with per-block fp32 scales
+ * (replaces torch-ext/finegrained_fp8_helion/fp8.py:19-39 and the dtype cast of
+ * torch-ext/finegrained_fp8_helion/__init__.py:14).
+ *
+ *   A  [M, K] float8_e4m3fn, row stride lda        B  [N, K] float8_e4m3fn, row stride ldb
+ *   As [M, ceil(K/128)] fp32, row stride ld_as     Bs [ceil(N/128), ceil(K/128)] fp32, row stride ld_bs
+ *   C  [M, N] bf16 (B200FP8_OUT_BF16) or fp32 (B200FP8_OUT_FP32), row stride ldc
+ *
+ *   C[m, n] = sum over 128-wide K blocks kb of
+ *             dot(A[m, kb], B[n, kb]) * As[m, kb] * Bs[n / 128, kb]       (fp32 accumulate)
+ *
+ * Requires lda % 16 == 0, ldb % 16 == 0, A and B 16-byte aligned (TMA rules);
+ * M, N, K otherwise arbitrary (ragged edges are masked). M == 0 or N == 0 is a
+ * no-op; K == 0 writes zeros.
+ *
+ * `workspace` is only used by B200FP8_VARIANT_STREAMK (and by AUTO when it picks
+ * that variant); size it with b200fp8_gemm_workspace_bytes for the same
+ * (M, N, K, variant). Its contents need no initialisation.
+ */
+int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs, void* C,
+                 int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc,
+                 int out_dtype, int variant,
+                 void* workspace, size_t workspace_bytes,
+                 uint32_t* status_word, void* stream);
+
+/* Bytes of workspace b200fp8_gemm needs for this call (0 when none). Negative = error status, negated. */
+int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
+
+/* The variant B200FP8_VARIANT_AUTO resolves to for this shape on the current device. */
+int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FP8_H_ */
