@@ -243,6 +243,14 @@ int b200fp8_quant_weight(const void* w, void* q, float* s, int64_t N, int64_t K,
   return launch_status();
 }
 
+int64_t b200fp8_streamk_first_unit(int64_t cta, int64_t total, int64_t grid) {
+  return streamk_first_unit(cta, total, grid);
+}
+int64_t b200fp8_streamk_owner(int64_t unit, int64_t total, int64_t grid) { return streamk_owner(unit, total, grid); }
+int64_t b200fp8_streamk_grid(int64_t M, int64_t N, int64_t K) {
+  return streamk_plan(M, N, K, sm_count_or_default()).grid;
+}
+
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) { return pick_variant(M, N, K, sm_count_or_default()); }
 
 int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
@@ -299,6 +307,9 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
     args.ldc = ldc;
     args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
     args.status_word = status_word;
+#ifdef B200FP8_TRACE
+    args.trace = reinterpret_cast<long long*>(workspace);  // trace builds reuse the (otherwise unused) workspace pointer
+#endif
     return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(A, B, args, lda, ldb, dev->sm_count, stream)
                                               : launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream);
   }
@@ -338,7 +349,8 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
     default: st = launch_streamk<256>(A, B, args, lda, ldb, p.grid, stream); break;
   }
   if (st != B200FP8_OK) return st;
-  streamk_fixup_kernel<<<static_cast<int>(p.num_tiles), 128, 0, stream>>>(
+  const dim3 fix_grid(static_cast<unsigned>(p.num_tiles), static_cast<unsigned>((M + kFixupRows - 1) / kFixupRows));
+  streamk_fixup_kernel<<<fix_grid, 128, 0, stream>>>(
       partial, C, M, N, p.num_kb, ldc, out_dtype == B200FP8_OUT_FP32, p.mp, p.grid);
   return launch_status();
 }

@@ -42,13 +42,16 @@ struct StreamKCfg {
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
-  static constexpr int SC_RING = STAGES + 4;  // see the note at the epilogue's TMEM release
+  static constexpr int TMEM_STAGES_RAW = 512 / MP_;
+  static constexpr int TMEM_STAGES = TMEM_STAGES_RAW > 8 ? 8 : TMEM_STAGES_RAW;  // accumulator stages in TMEM
+  static constexpr int SC_RING = STAGES + TMEM_STAGES + 2;  // see the note at the epilogue's TMEM release
   static constexpr int SC_BYTES = MP_ * 4;
+  static constexpr int PRODUCER_BATCH = STAGES >= 8 ? 4 : (STAGES >= 4 ? 2 : 1);
   static constexpr int EPI_WARPS = MP_ >= 128 ? 8 : 4;
   static constexpr int EPI_COLS = MP_ / (EPI_WARPS / 4);
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   static constexpr bool REBALANCE_REGS = (EPI_COLS > 64);
-  static constexpr int TMEM_COLS = (2 * MP_) < 32 ? 32 : 2 * MP_;
+  static constexpr int TMEM_COLS = TMEM_STAGES * MP_;  // 128, 256 or 512: a power of two >= 32
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_RING * SC_BYTES + BAR_BYTES + 1024;
 };
@@ -86,6 +89,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   using Cfg = StreamKCfg<MP>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int SC_RING = Cfg::SC_RING;
+  constexpr uint32_t TS = Cfg::TMEM_STAGES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,11 +98,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint64_t* full = bars;                            // [STAGES]
   uint64_t* empty = bars + STAGES;                  // [STAGES]
   uint64_t* sc_full = bars + 2 * STAGES;            // [SC_RING]
-  uint64_t* tfull = bars + 2 * STAGES + SC_RING;    // [2]
-  uint64_t* tempty = tfull + 2;                     // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* tfull = bars + 2 * STAGES + SC_RING;    // [TS]
+  uint64_t* tempty = tfull + TS;                    // [TS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + TS);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  static_assert((2 * STAGES + SC_RING + 4) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
+  static_assert((2 * STAGES + SC_RING + 2 * TS) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -109,7 +113,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       mbar_init(&empty[s], 1);
     }
     for (int s = 0; s < SC_RING; ++s) mbar_init(&sc_full[s], 1);
-    for (int s = 0; s < 2; ++s) {
+    for (uint32_t s = 0; s < TS; ++s) {
       mbar_init(&tfull[s], 1);
       mbar_init(&tempty[s], Cfg::EPI_WARPS);
     }
@@ -134,7 +138,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint32_t* status_word = args.status_word;
 
   if (warp < 4) {
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<40>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<56>();
   }
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -145,20 +149,40 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const uint64_t pol_keep = policy_evict_last();     // the few activation rows are re-read by every CTA
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t u = u0; u < u1; ++u, ++it) {
-        const int64_t tile = u / num_kb;
-        const int kb = static_cast<int>(u - tile * num_kb);
-        const uint32_t s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status_word)) { ok = false; break; }
-        uint8_t* w_dst = smem + s * Cfg::STAGE_BYTES;
-        uint8_t* x_dst = w_dst + Cfg::W_BYTES;
-        mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(w_dst, &tmap_w, &full[s], kb * Cfg::BK, static_cast<int32_t>(tile * Cfg::BN), pol_stream);
-        tma_load_2d_hint(x_dst, &tmap_x, &full[s], kb * Cfg::BK, 0, pol_keep);
-        const uint32_t r = it % SC_RING;
-        mbar_arrive_expect_tx(&sc_full[r], Cfg::SC_BYTES);
-        bulk_load_1d(sc_ring + r * MP, args.AsT + static_cast<int64_t>(kb) * MP, Cfg::SC_BYTES, &sc_full[r]);
+      // Units are issued in batches of up to kBatch consecutive K blocks: the batch's loads
+      // go out back to back, so that DRAM sees kBatch * 128 contiguous bytes of each weight
+      // row within one burst of requests instead of 128-byte pieces spread over time.
+      constexpr int kBatch = Cfg::PRODUCER_BATCH;
+      for (int64_t u = u0; ok && u < u1;) {
+        const int64_t left = u1 - u;
+        const int nb = left < kBatch ? static_cast<int>(left) : kBatch;
+        for (int i = 0; i < nb; ++i) {
+          const uint32_t j = it + i;
+          if (!mbar_wait(&empty[j % STAGES], ((j / STAGES) & 1u) ^ 1u, abort_flag, status_word)) { ok = false; break; }
+        }
+        if (!ok) break;
+        for (int i = 0; i < nb; ++i) {
+          const uint32_t j = it + i;
+          const int64_t tile = (u + i) / num_kb;
+          const int kb = static_cast<int>((u + i) - tile * num_kb);
+          const uint32_t s = j % STAGES;
+          uint8_t* w_dst = smem + s * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(w_dst, &tmap_w, &full[s], kb * Cfg::BK, static_cast<int32_t>(tile * Cfg::BN), pol_stream);
+        }
+        for (int i = 0; i < nb; ++i) {
+          const uint32_t j = it + i;
+          const int64_t tile = (u + i) / num_kb;
+          const int kb = static_cast<int>((u + i) - tile * num_kb);
+          const uint32_t s = j % STAGES;
+          uint8_t* x_dst = smem + s * Cfg::STAGE_BYTES + Cfg::W_BYTES;
+          tma_load_2d_hint(x_dst, &tmap_x, &full[s], kb * Cfg::BK, 0, pol_keep);
+          const uint32_t r = j % SC_RING;
+          mbar_arrive_expect_tx(&sc_full[r], Cfg::SC_BYTES);
+          bulk_load_1d(sc_ring + r * MP, args.AsT + static_cast<int64_t>(kb) * MP, Cfg::SC_BYTES, &sc_full[r]);
+        }
+        it += nb;
+        u += nb;
       }
       if (!ok) {
         const uint32_t first = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
@@ -180,8 +204,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       for (int64_t u = u0; u < u1; ++u, ++it) {
         const uint32_t s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
-        const uint32_t ts = it & 1u;
-        const uint32_t tph = (it >> 1) & 1u;
+        const uint32_t ts = it % TS;
+        const uint32_t tph = (it / TS) & 1u;
         if (!mbar_wait(&tempty[ts], tph ^ 1u, abort_flag, status_word)) { ok = false; break; }
         if (!mbar_wait(&full[s], ph, abort_flag, status_word)) { ok = false; break; }
         tc_fence_after();
@@ -197,14 +221,14 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if (!ok && it > 0) {
         const uint32_t j = it - 1;
         const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&tfull[j & 1u], (j >> 1) & 1u)) {
+        while (!mbar_try_wait(&tfull[j % TS], (j / TS) & 1u)) {
           if (globaltimer_ns() - t0 > kWaitLimitNs) break;
         }
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ promotion + epilogue
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<232>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<224>();
     constexpr int EC = Cfg::EPI_COLS;
     const int e = warp - 4;
     const int q = warp & 3;
@@ -215,6 +239,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     float acc[EC];
     int seg_first_kb = 0;
     bool seg_is_first = true;
+    float sb_next = 0.f;
+    if (u0 < u1) sb_next = __ldg(args.Bs + (u0 / num_kb) * args.ld_bs + (u0 % num_kb));
     for (int64_t u = u0; u < u1; ++u, ++it) {
       const int64_t tile = u / num_kb;
       const int kb = static_cast<int>(u - tile * num_kb);
@@ -224,9 +250,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         seg_first_kb = kb;
         seg_is_first = (u == u0);
       }
-      const float sb = __ldg(args.Bs + tile * args.ld_bs + kb);
-      const uint32_t ts = it & 1u;
-      const uint32_t tph = (it >> 1) & 1u;
+      const float sb = sb_next;  // weight-block scale of this unit, fetched one unit ahead
+      if (u + 1 < u1) sb_next = __ldg(args.Bs + ((u + 1) / num_kb) * args.ld_bs + ((u + 1) % num_kb));
+      const uint32_t ts = it % TS;
+      const uint32_t tph = (it / TS) & 1u;
       const uint32_t r = it % SC_RING;
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word) &&
                                        mbar_wait(&sc_full[r], (it / SC_RING) & 1u, abort_flag, status_word));
@@ -257,9 +284,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           tmem_ld_wait();
           if (c + 32 == EC) {
             // The TMEM stage is handed back before the scale reads below. The MMA warp
-            // can then run at most 2 units ahead of this warp and the producer at most
-            // STAGES units ahead of the MMA warp, so a scale slot is rewritten no
-            // earlier than STAGES + 3 units later: SC_RING = STAGES + 4 slots suffice.
+            // can then run at most TS units ahead of this warp and the producer at most
+            // STAGES units ahead of the MMA warp, so a scale slot is rewritten no earlier
+            // than STAGES + TS + 1 units later: SC_RING = STAGES + TS + 2 slots suffice.
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[ts]);
@@ -313,8 +340,12 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   }
 }
 
-// One CTA of 128 threads per weight tile; tiles that a single CTA of the stream-K
-// kernel covered completely were already written and are skipped.
+// Adds the pieces of every split tile. Grid = (weight tiles, ceil(M / 8)); a CTA of 128
+// threads (one per weight row of the tile) sums 8 token rows, pieces in ascending CTA order.
+// Tiles that a single CTA of the stream-K kernel covered completely were already written
+// and are skipped.
+constexpr int kFixupRows = 8;
+
 __global__ void __launch_bounds__(128)
 streamk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
                      int out_fp32, int MP, int64_t sk_grid) {
@@ -326,18 +357,27 @@ streamk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int6
   if (c_first == c_last) return;
   const int64_t n = tile * 128 + threadIdx.x;
   if (n >= N) return;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kFixupRows;
   const int64_t slot_elems = static_cast<int64_t>(MP) * 128;
-  for (int64_t m = 0; m < M; ++m) {
-    float sum = 0.f;
-    for (int64_t c = c_first; c <= c_last; ++c) {
-      const int64_t first_tile_of_c = streamk_first_unit(c, total, sk_grid) / num_kb;
-      const int64_t slot = 2 * c + (first_tile_of_c == tile ? 0 : 1);
-      sum += partial[slot * slot_elems + m * 128 + threadIdx.x];
+  float sum[kFixupRows];
+#pragma unroll
+  for (int i = 0; i < kFixupRows; ++i) sum[i] = 0.f;
+  for (int64_t c = c_first; c <= c_last; ++c) {
+    const int64_t first_tile_of_c = streamk_first_unit(c, total, sk_grid) / num_kb;
+    const int64_t slot = 2 * c + (first_tile_of_c == tile ? 0 : 1);
+    const float* src = partial + slot * slot_elems + m0 * 128 + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < kFixupRows; ++i)
+      if (m0 + i < M) sum[i] += __ldg(src + i * 128);
+  }
+#pragma unroll
+  for (int i = 0; i < kFixupRows; ++i) {
+    if (m0 + i < M) {
+      if (out_fp32)
+        reinterpret_cast<float*>(C)[(m0 + i) * ldc + n] = sum[i];
+      else
+        reinterpret_cast<__nv_bfloat16*>(C)[(m0 + i) * ldc + n] = __float2bfloat16_rn(sum[i]);
     }
-    if (out_fp32)
-      reinterpret_cast<float*>(C)[m * ldc + n] = sum;
-    else
-      reinterpret_cast<__nv_bfloat16*>(C)[m * ldc + n] = __float2bfloat16_rn(sum);
   }
 }
 

@@ -6,14 +6,15 @@
 //   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per K block
 //               into a STAGES-deep shared-memory ring (SWIZZLE_128B, no multicast)
 //   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block into
-//               one of two TMEM accumulator stages, then tcgen05.commit to release the
+//               one of the TMEM accumulator stages, then tcgen05.commit to release the
 //               smem slot and to publish the TMEM stage
 //   warp 2      TMEM allocation / deallocation
 //   warps 4..   promotion + epilogue: tcgen05.ld the fp32 partial of one K block,
 //               acc += partial * (As[row, kb] * Bs[nb, kb]) in registers (the block
 //               scales are arbitrary fp32, so partial sums cannot stay in TMEM across
 //               K blocks), and after the last K block convert and store the tile.
-// The two TMEM stages let the MMA of K block k+1 overlap the promotion of block k.
+// Several TMEM accumulator stages (512 / BN) let the MMAs of later K blocks overlap the
+// promotion of block k.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -21,6 +22,18 @@
 #include "ptx.cuh"
 
 namespace b200fp8 {
+
+// Optional event trace for performance work (compiled in only with -DB200FP8_TRACE):
+// CTA 0 records clock64 stamps of its role loops for K-block indices [40, 56).
+#ifdef B200FP8_TRACE
+#define B200FP8_TRACE_EVENT(role, idx, tag)                                                          \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) >= 40u && (idx) < 56u && args.trace)     \
+      args.trace[((role) * 16 + ((idx) - 40u)) * 8 + (tag)] = clock64();                              \
+  } while (0)
+#else
+#define B200FP8_TRACE_EVENT(role, idx, tag) do { } while (0)
+#endif
 
 struct GemmArgs {
   const float* As;
@@ -30,6 +43,9 @@ struct GemmArgs {
   int64_t ld_as, ld_bs, ldc;
   int out_fp32;
   uint32_t* status_word;
+#ifdef B200FP8_TRACE
+  long long* trace;
+#endif
 };
 
 template <int BN_>
@@ -48,7 +64,9 @@ struct TileCfg {
   static constexpr int A_BYTES = BM * BK;
   static constexpr int B_BYTES = BN_ * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN_;
+  static constexpr int ISSUERS = 2;                 // MMA issuer warps; issuer p takes the K blocks with index = p (mod 2)
+  static constexpr int TMEM_STAGES = 512 / BN_;     // accumulator stages in TMEM (all 512 columns are used)
+  static constexpr int TMEM_COLS = TMEM_STAGES * BN_;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
 };
@@ -59,15 +77,17 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmArgs args) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr uint32_t TS = Cfg::TMEM_STAGES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
   uint64_t* full = bars;                  // [STAGES]  TMA bytes landed
   uint64_t* empty = bars + STAGES;        // [STAGES]  MMA finished reading the slot
-  uint64_t* tfull = bars + 2 * STAGES;    // [2]       TMEM stage holds a finished K-block partial
-  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]    every epilogue warp has read the TMEM stage
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* tfull = bars + 2 * STAGES;    // [TS]      TMEM stage holds a finished K-block partial
+  uint64_t* tempty = bars + 2 * STAGES + TS;  // [TS]  every epilogue warp has read the TMEM stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * TS);
+  static_assert((2 * STAGES + 2 * TS) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -78,7 +98,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (uint32_t s = 0; s < TS; ++s) {
       mbar_init(&tfull[s], 1);
       mbar_init(&tempty[s], Cfg::EPI_WARPS);
     }
@@ -102,7 +122,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint32_t* status_word = args.status_word;
 
   if (warp < 4) {
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<40>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<56>();
   }
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -117,12 +137,15 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
+          B200FP8_TRACE_EVENT(0, it, 0);
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status_word)) { ok = false; break; }
+          B200FP8_TRACE_EVENT(0, it, 1);
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
           tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+          B200FP8_TRACE_EVENT(0, it, 2);
         }
       }
       if (!ok) {
@@ -136,25 +159,41 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(128, BN);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          const uint32_t ts = it & 1u;
-          const uint32_t tph = (it >> 1) & 1u;
-          if (!mbar_wait(&tempty[ts], tph ^ 1u, abort_flag, status_word)) { ok = false; break; }
-          if (!mbar_wait(&full[s], ph, abort_flag, status_word)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
-          const uint64_t a_desc = make_smem_desc_sw128(a_addr);
-          const uint64_t b_desc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
-          const uint32_t d_tmem = tmem_base + ts * BN;
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Issuing the four tcgen05.mma of a K block, the two commits and the two barrier waits
+    // costs an issuer some 650 clocks, while the tensor pipe needs 512 (BN = 256) or 256
+    // (BN = 128) for that block. Two issuer warps therefore alternate: issuer p takes the
+    // K blocks whose running index is p (mod 2). Consecutive K blocks use different smem
+    // slots and different TMEM stages, so the two instruction streams are independent.
+    // The whole warp runs the loop (addresses stay warp-uniform) and one elected lane issues.
+    const uint32_t p = (warp == 1) ? 0u : 1u;
+    constexpr uint32_t idesc = make_idesc_e4m3_f32(128, BN);
+    const uint32_t smem_base = smem_u32(smem);
+    uint32_t it = 0;
+    uint32_t last = 0xffffffffu;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((it & 1u) != p) continue;
+        const uint32_t s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        const uint32_t ts = it % TS;
+        const uint32_t tph = (it / TS) & 1u;
+        // operands first (they land long before), then the TMEM stage: nothing but the issue
+        // itself is left to do once the epilogue hands the stage back
+        const uint32_t a_addr = smem_base + s * Cfg::STAGE_BYTES;
+        const uint64_t a_desc = make_smem_desc_sw128(a_addr);
+        const uint64_t b_desc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
+        const uint32_t d_tmem = tmem_base + ts * BN;
+        B200FP8_TRACE_EVENT(1, it, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, abort_flag, status_word));
+        B200FP8_TRACE_EVENT(1, it, 1);
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(&tempty[ts], tph ^ 1u, abort_flag, status_word));
+        B200FP8_TRACE_EVENT(1, it, 2);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < Cfg::BK / 32; ++k) {
             // +2 in the start-address field = +32 bytes = one K=32 slice of e4m3
@@ -163,22 +202,24 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tc_commit(&empty[s]);
           tc_commit(&tfull[ts]);
         }
+        __syncwarp();
+        B200FP8_TRACE_EVENT(1, it, 3);
+        last = it;
       }
-      if (!ok && it > 0) {
-        // Abort path: bounded wait for the MMAs already issued.
-        const uint32_t j = it - 1;
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&tfull[j & 1u], (j >> 1) & 1u)) {
-          if (globaltimer_ns() - t0 > kWaitLimitNs) break;
-        }
+    }
+    if (!ok && last != 0xffffffffu && lane == 0) {
+      // Abort path: bounded wait for the MMAs this warp already issued.
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&tfull[last % TS], (last / TS) & 1u)) {
+        if (globaltimer_ns() - t0 > kWaitLimitNs) break;
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ promotion + epilogue
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<232>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<224>();
     const int e = warp - 4;
     const int q = warp & 3;           // TMEM lane quarter this warp may read
-    const int cw = e >> 2;            // which 64-column slice of the tile
+    const int cw = e >> 2;            // which EPI_COLS-wide column slice of the tile
     const int num_nb = static_cast<int>((N + 127) / 128);
     uint32_t it = 0;
     bool ok = true;
@@ -193,61 +234,114 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const float* as_row = args.As + row_c * args.ld_as;
       const float* bs_row = args.Bs + static_cast<int64_t>(nb) * args.ld_bs;
 
-      float acc[Cfg::EPI_COLS];
+      // accumulators as 32-column groups of packed pairs: acc[g][j] = columns 32 g + 2 j, + 1
+      float2 acc[Cfg::EPI_COLS / 32][16];
 #pragma unroll
-      for (int j = 0; j < Cfg::EPI_COLS; ++j) acc[j] = 0.f;
+      for (int g = 0; g < Cfg::EPI_COLS / 32; ++g)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[g][j] = make_float2(0.f, 0.f);
 
-      float sc_next = __ldg(as_row) * __ldg(bs_row);
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const float sc = sc_next;
-        if (kb + 1 < num_kb) sc_next = __ldg(as_row + kb + 1) * __ldg(bs_row + kb + 1);
-        const uint32_t ts = it & 1u;
-        const uint32_t tph = (it >> 1) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word));
-        if (!ok) break;
+      // One K block: wait for its partial in TMEM, pull it into registers in 32-column
+      // chunks (the tcgen05.ld of chunk g + 1 is in flight while the FMAs of chunk g
+      // issue), hand the TMEM stage back as soon as the last chunk has landed.
+      auto promote = [&](float sc) -> bool {
+        const uint32_t ts = it % TS;
+        const uint32_t tph = (it / TS) & 1u;
+        const uint32_t tr_it = it, tr_role = (warp == 4) ? 2u : ((warp == 8) ? 3u : 99u);
+        (void)tr_it; (void)tr_role;
+        ++it;
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 0);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word))) return false;
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ts * BN + cw * Cfg::EPI_COLS;
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
+        // Two tcgen05.ld (32 columns each) are kept in flight; the TMEM stage is handed
+        // back as soon as the last chunk has landed in registers, before its FMAs.
+        uint32_t pa[32], pb[32];
+        constexpr int CHUNKS = Cfg::EPI_COLS / 32;
+        tmem_ld_32x32(taddr, pa);
+        tmem_ld_32x32(taddr + 32, pb);
+        tmem_ld_wait_32(pa);
+        tmem_ld_wait_32(pb);
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
 #pragma unroll
-        for (int c = 0; c < Cfg::EPI_COLS; c += 64) {
-          uint32_t p0[32], p1[32];
-          tmem_ld_32x32(taddr + c, p0);
-          tmem_ld_32x32(taddr + c + 32, p1);
-          tmem_ld_wait();
-          if (c + 64 == Cfg::EPI_COLS) {
-            // the whole slice of this TMEM stage is in registers: hand the stage back
+        for (int g = 0; g < CHUNKS; g += 2) {
+          const bool more = g + 2 < CHUNKS;
+          if (!more) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[ts]);
+            if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
           }
+          fma32_scalar(acc[g], pa, sc);
+          if (g == 0 && tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 5);
+          if (more) tmem_ld_32x32(taddr + (g + 2) * 32, pa);
+          fma32_scalar(acc[g + 1], pb, sc);
+          if (more) {
+            tmem_ld_32x32(taddr + (g + 3) * 32, pb);
+            tmem_ld_wait_32(pa);
+            tmem_ld_wait_32(pb);
+          }
+          if (g == 0 && tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 6);
+        }
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 7);
+        return true;
+      };
+
+      // The scales As[row, kb] and Bs[nb, kb] come from global memory (L2 latency of several
+      // hundred clocks). They are fetched a whole group of PF K blocks ahead so that their
+      // first use never stalls the promotion loop.
+      constexpr int PF = 4;
+      float sa_c[PF], sb_c[PF], sa_n[PF], sb_n[PF];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(__uint_as_float(p0[j]), sc, acc[c + j]);
+      for (int j = 0; j < PF; ++j) {
+        const int k = j < num_kb ? j : num_kb - 1;
+        sa_c[j] = __ldg(as_row + k);
+        sb_c[j] = __ldg(bs_row + k);
+      }
+      for (int kb0 = 0; ok && kb0 < num_kb; kb0 += PF) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c + 32 + j] = fmaf(__uint_as_float(p1[j]), sc, acc[c + 32 + j]);
+        for (int j = 0; j < PF; ++j) {
+          int k = kb0 + PF + j;
+          k = k < num_kb ? k : num_kb - 1;
+          sa_n[j] = __ldg(as_row + k);
+          sb_n[j] = __ldg(bs_row + k);
+        }
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+          if (ok && kb0 + j < num_kb) ok = promote(sa_c[j] * sb_c[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+          sa_c[j] = sa_n[j];
+          sb_c[j] = sb_n[j];
         }
       }
       if (!ok) break;
 
+#define ACC(i) (((i) & 1) ? acc[(i) >> 5][((i) & 31) >> 1].y : acc[(i) >> 5][((i) & 31) >> 1].x)
       if (row < M && col0 < N) {
         if (args.out_fp32) {
           float* crow = reinterpret_cast<float*>(args.C) + row * args.ldc + col0;
           if (col0 + Cfg::EPI_COLS <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
 #pragma unroll
             for (int j = 0; j < Cfg::EPI_COLS; j += 4)
-              *reinterpret_cast<float4*>(crow + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+              *reinterpret_cast<float4*>(crow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
           } else {
 #pragma unroll
             for (int j = 0; j < Cfg::EPI_COLS; ++j)
-              if (col0 + j < N) crow[j] = acc[j];
+              if (col0 + j < N) crow[j] = ACC(j);
           }
         } else {
           __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + row * args.ldc + col0;
           if (col0 + Cfg::EPI_COLS <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
 #pragma unroll
             for (int j = 0; j < Cfg::EPI_COLS; j += 8) {
-              __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[j], acc[j + 1]);
-              __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[j + 2], acc[j + 3]);
-              __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[j + 4], acc[j + 5]);
-              __nv_bfloat162 v3 = __floats2bfloat162_rn(acc[j + 6], acc[j + 7]);
+              __nv_bfloat162 v0 = __floats2bfloat162_rn(ACC(j), ACC(j + 1));
+              __nv_bfloat162 v1 = __floats2bfloat162_rn(ACC(j + 2), ACC(j + 3));
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(ACC(j + 4), ACC(j + 5));
+              __nv_bfloat162 v3 = __floats2bfloat162_rn(ACC(j + 6), ACC(j + 7));
               uint4 u;
               u.x = *reinterpret_cast<uint32_t*>(&v0);
               u.y = *reinterpret_cast<uint32_t*>(&v1);
@@ -258,12 +352,13 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
 #pragma unroll
             for (int j = 0; j < Cfg::EPI_COLS; ++j)
-              if (col0 + j < N) crow[j] = __float2bfloat16_rn(acc[j]);
+              if (col0 + j < N) crow[j] = __float2bfloat16_rn(ACC(j));
           }
         }
       }
     }
   }
+#undef ACC
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();

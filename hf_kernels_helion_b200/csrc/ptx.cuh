@@ -78,29 +78,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in these kernels is bounded: after kWaitLimitNs without the phase
-// completing, the waiter raises the CTA-wide abort flag (shared memory), records
-// B200FP8_DEV_WAIT_TIMEOUT in the caller's status word and returns false; every
-// role loop then falls through to the common teardown (drain own TMA copies with a
-// bounded wait, free TMEM, return).
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Every wait in these kernels is bounded: after about kWaitLimitClks SM clocks (two
+// seconds at 2 GHz) without the phase completing, the waiter raises the CTA-wide abort
+// flag (shared memory), records B200FP8_DEV_WAIT_TIMEOUT in the caller's status word and
+// returns false; every role loop then falls through to the common teardown (drain own
+// TMA copies with a bounded wait, free TMEM, return). The clock is only looked at every
+// 1024 polls so that the common case costs nothing but the try_wait itself.
+constexpr long long kWaitLimitClks = 4000000000ll;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // used by the abort-path drains
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status_word) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (((++spins) & 63u) == 0u) {
+    if (((++spins) & 1023u) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitClks) {
         *abort_flag = 1u;
         if (status_word != nullptr) atomicExch(status_word, 1u);
         return false;
       }
     }
   }
+}
+
+// Warp-wide wait: lane 0 polls, the result is broadcast (one mbarrier transaction per
+// poll instead of 32). Must be called by all 32 lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t* status_word) {
+  uint32_t ok = 1u;
+  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag, status_word) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
 }
 
 // ----------------------------------------------------------------------------- TMA (tiled, 2-D, no multicast)
@@ -219,6 +233,37 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+
+// tcgen05.wait::ld for one 32-register load, with the registers threaded through the
+// statement as read-write operands so that the compiler cannot schedule a use of
+// them above the wait.
+__device__ __forceinline__ void tmem_ld_wait_32(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+        "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+        "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+      :
+      : "memory");
+}
+
+// acc[0..31] += p[0..31] * s with packed two-wide fp32 FMAs (fma.rn.f32x2, sm_100).
+__device__ __forceinline__ void fma32_scalar(float2 (&acc)[16], const uint32_t (&p)[32], float s) {
+  const float2 s2 = make_float2(s, s);
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    acc[j] = __ffma2_rn(make_float2(__uint_as_float(p[2 * j]), __uint_as_float(p[2 * j + 1])), s2, acc[j]);
 }
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {

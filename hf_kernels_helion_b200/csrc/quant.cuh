@@ -29,15 +29,32 @@ __device__ __forceinline__ float amax8(const uint4& v) {
   return m;
 }
 
+// x / scale for the e4m3 cast, bit-identical to e4m3_rne(__fdiv_rn(x, scale)) but without
+// a division per element. q = x * rcp (rcp = 1 / scale, correctly rounded) is within
+// 2 ulp of the IEEE quotient; the cast to e4m3 can only differ if a rounding boundary
+// of e4m3 lies between the two, i.e. if q sits within a few ulp of a tie (fp32
+// mantissa bits below the three kept ones equal to 0x80000). Those rare elements, the
+// e4m3 subnormal range (different tie positions) and non-finite / out-of-range q take
+// the exact division instead.
+__device__ __forceinline__ float quotient_for_cast(float x, float scale, float rcp) {
+  const float q = x * rcp;
+  const uint32_t mag = __float_as_uint(q) & 0x7FFFFFFFu;
+  const bool near_tie = ((mag & 0xFFFFFu) - (0x80000u - 8u)) <= 16u;
+  const bool odd_range = mag >= 0x43E80000u /* 464, inf, NaN */ || mag < 0x3C800000u /* 2^-6 */;
+  if ((near_tie || odd_range) && mag != 0u) return __fdiv_rn(x, scale);  // a zero product casts to the same zero
+  return q;
+}
+
 // 8 bf16 (one uint4) divided by `scale` and packed into 8 e4m3 bytes (one uint2).
 // scale == 0 (all-zero group) yields zero bytes instead of the 0/0 NaN of the formula.
 __device__ __forceinline__ uint2 quant8(const uint4& v, float scale) {
   if (scale == 0.f) return make_uint2(0u, 0u);
+  const float rcp = __frcp_rn(scale);
   uint2 o;
-  o.x = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.x), scale), __fdiv_rn(bf16_hi(v.x), scale)) |
-        (cvt_e4m3x2(__fdiv_rn(bf16_lo(v.y), scale), __fdiv_rn(bf16_hi(v.y), scale)) << 16);
-  o.y = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.z), scale), __fdiv_rn(bf16_hi(v.z), scale)) |
-        (cvt_e4m3x2(__fdiv_rn(bf16_lo(v.w), scale), __fdiv_rn(bf16_hi(v.w), scale)) << 16);
+  o.x = cvt_e4m3x2(quotient_for_cast(bf16_lo(v.x), scale, rcp), quotient_for_cast(bf16_hi(v.x), scale, rcp)) |
+        (cvt_e4m3x2(quotient_for_cast(bf16_lo(v.y), scale, rcp), quotient_for_cast(bf16_hi(v.y), scale, rcp)) << 16);
+  o.y = cvt_e4m3x2(quotient_for_cast(bf16_lo(v.z), scale, rcp), quotient_for_cast(bf16_hi(v.z), scale, rcp)) |
+        (cvt_e4m3x2(quotient_for_cast(bf16_lo(v.w), scale, rcp), quotient_for_cast(bf16_hi(v.w), scale, rcp)) << 16);
   return o;
 }
 

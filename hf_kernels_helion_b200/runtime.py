@@ -86,7 +86,6 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
     if out_dtype not in _OUT_CODES:
         raise ValueError(f"output dtype must be torch.bfloat16 or torch.float32, got {out_dtype}")
     for name, t in (("A", A), ("B", B), ("As", As), ("Bs", Bs)):
-        _require_cuda(t, name)
         if t.dim() != 2:
             raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
         if t.device != A.device:
@@ -105,6 +104,7 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
     if tuple(Bs.shape) != (nblocks, kblocks):
         raise ValueError(f"Bs must be [ceil(N/128), ceil(K/128)] = [{nblocks}, {kblocks}], got {tuple(Bs.shape)}")
 
+    _require_cuda(A, "A")
     dev = A.device
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
@@ -136,13 +136,13 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
 
 
 def _quant_common(x: torch.Tensor, name: str):
-    _require_cuda(x, name)
     if x.dim() != 2:
         raise ValueError(f"{name} must be 2-D, got shape {tuple(x.shape)}")
     if x.dtype != torch.bfloat16:
         raise ValueError(f"{name} must be torch.bfloat16, got {x.dtype}")
     if x.shape[1] % 8 != 0:
         raise ValueError(f"K = {x.shape[1]} must be a multiple of 8")
+    _require_cuda(x, name)
     return _row_major(x, 8)
 
 

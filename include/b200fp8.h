@@ -133,6 +133,17 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
 /* The variant B200FP8_VARIANT_AUTO resolves to for this shape on the current device. */
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K);
 
+/*
+ * Work partition of the stream-K variant, exposed for tests and tools (no counterpart
+ * in the reference). `total` (weight tile, K block) units are spread over `grid` CTAs in
+ * contiguous ranges: CTA c owns units [first_unit(c), first_unit(c + 1)).
+ * b200fp8_streamk_grid returns the CTA count b200fp8_gemm would use on the current device
+ * (or on a 148-SM B200 when no device is present).
+ */
+int64_t b200fp8_streamk_first_unit(int64_t cta, int64_t total, int64_t grid);
+int64_t b200fp8_streamk_owner(int64_t unit, int64_t total, int64_t grid);
+int64_t b200fp8_streamk_grid(int64_t M, int64_t N, int64_t K);
+
 #ifdef __cplusplus
 }
 #endif

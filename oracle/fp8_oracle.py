@@ -193,6 +193,21 @@ def max_err_over_rms(out: torch.Tensor, ref: torch.Tensor) -> float:
     return float((out.to(torch.float64) - ref).abs().max().item() / rms)
 
 
+def bf16_ulp_error(out_bf16: torch.Tensor, ref_fp32: torch.Tensor, noise: float = 2e-5) -> float:
+    """Largest |out - ref| measured in bf16 units in the last place OF THE REFERENCE VALUE,
+    after allowing `noise * rms(ref)` of absolute slack for fp32 summation-order
+    differences (they dominate for elements that cancel to nearly zero, where one bf16 ulp
+    is far below the fp32 noise of the sum).  A correctly rounded bf16 output gives <= 0.5;
+    "within one bf16 ulp" means <= 1."""
+    ref = ref_fp32.to(torch.float64)
+    out = out_bf16.to(torch.float64)
+    rms = ref.pow(2).mean().sqrt().item()
+    mag = ref.abs().clamp_min(1e-300)
+    ulp = torch.exp2(torch.floor(torch.log2(mag)) - 7.0)
+    err = ((out - ref).abs() - noise * rms).clamp_min(0.0) / ulp
+    return float(err.max().item())
+
+
 def bf16_ulp_distance(out_bf16: torch.Tensor, ref_fp32: torch.Tensor) -> torch.Tensor:
     """Distance, in bf16 units in the last place, between a bf16 tensor and bf16(ref)."""
     a = out_bf16.contiguous().view(torch.int16).to(torch.int32)

@@ -1,0 +1,54 @@
+"""N-sharded tensor-parallel GEMM on real GPUs over NCCL (skipped with fewer than 2 GPUs)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import fp8_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from hf_kernels_helion_b200 import runtime, tp
+
+        M, N, K = 640, 256 * world, 1024
+        A, B, As, Bs = oracle.make_quantised_inputs(M, N, K, 0)
+        dev = torch.device("cuda", rank)
+        lin = tp.ShardedFp8Linear.from_full(B.to(dev), Bs.to(dev))
+        out = lin(A.to(dev), As.to(dev), torch.bfloat16)
+        runtime.check_device_status()
+        ref = oracle.gemm_dequant(A, B, As, Bs)
+        ok = out.shape == (M, N) and oracle.bf16_ulp_error(out.cpu(), ref) <= 1
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_linear_nccl():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert dict(q.get(timeout=5) for _ in range(world)) == {r: True for r in range(world)}
