@@ -27,6 +27,8 @@ SIGNATURES = {
                              c_void_p]),
     "b200fp8_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
     "b200fp8_gemm_pick_variant": (c_int, [c_int64, c_int64, c_int64]),
+    "b200fp8_gemm_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                           c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b200fp8_streamk_first_unit": (c_int64, [c_int64, c_int64, c_int64]),
     "b200fp8_streamk_owner": (c_int64, [c_int64, c_int64, c_int64]),
     "b200fp8_streamk_grid": (c_int64, [c_int64, c_int64, c_int64]),

@@ -105,6 +105,29 @@ int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200FP8_OK : B200FP8_ERR_LAUNCH; }
 
+// Scratch of b200fp8_gemm_decode_static: lives in the module image of every device that
+// loads the library, from load until process exit. In host code the NAME of a __device__
+// array is only a host-side stand-in, not a device address; the address a kernel may use
+// comes from cudaGetSymbolAddress, taken once per device with that device current.
+constexpr size_t kStaticScratchBytes = B200FP8_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];
+
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200FP8_ERR_ARCH;
+  void* p = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return B200FP8_ERR_DRIVER;
+    }
+    g_static_scratch_addr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return B200FP8_OK;
+}
+
 int streamk_mp(int64_t M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
@@ -329,6 +352,67 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
     st = launch_status();
     if (st != B200FP8_OK) return st;
   }
+  StreamKArgs args;
+  args.Bs = Bs;
+  args.AsT = ast;
+  args.partial = partial;
+  args.C = C;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ld_bs = ld_bs;
+  args.ldc = ldc;
+  args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
+  args.status_word = status_word;
+  switch (p.mp) {
+    case 16: st = launch_streamk<16>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 32: st = launch_streamk<32>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 64: st = launch_streamk<64>(A, B, args, lda, ldb, p.grid, stream); break;
+    case 128: st = launch_streamk<128>(A, B, args, lda, ldb, p.grid, stream); break;
+    default: st = launch_streamk<256>(A, B, args, lda, ldb, p.grid, stream); break;
+  }
+  if (st != B200FP8_OK) return st;
+  const dim3 fix_grid(static_cast<unsigned>(p.num_tiles), static_cast<unsigned>((M + kFixupRows - 1) / kFixupRows));
+  streamk_fixup_kernel<<<fix_grid, 128, 0, stream>>>(
+      partial, C, M, N, p.num_kb, ldc, out_dtype == B200FP8_OUT_FP32, p.mp, p.grid);
+  return launch_status();
+}
+
+int b200fp8_gemm_decode_static(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M,
+                               int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs,
+                               int64_t ldc, int out_dtype, uint32_t* status_word, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
+  if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
+  if (M == 0 || N == 0) return B200FP8_OK;
+  if (M > 256) return B200FP8_ERR_TOO_LARGE;
+  if (A == nullptr || B == nullptr || As == nullptr || Bs == nullptr || C == nullptr) return B200FP8_ERR_NULL;
+  if (K == 0) return B200FP8_ERR_SHAPE;
+  const int64_t kblocks = (K + 127) / 128;
+  if (ldc < N || lda < K || ldb < K || ld_as < kblocks || ld_bs < kblocks) return B200FP8_ERR_SHAPE;
+  if (lda % 16 != 0 || ldb % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(B) & 15u) != 0)
+    return B200FP8_ERR_ALIGN;
+  if (N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
+
+  const DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  const StreamKPlan p = streamk_plan(M, N, K, dev->sm_count);
+  if (static_cast<size_t>(p.ast_bytes + p.partial_bytes) > kStaticScratchBytes) return B200FP8_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  st = static_scratch_address(&scratch);   // first call on a device: cudaGetSymbolAddress
+  if (st != B200FP8_OK) return st;
+  float* ast = static_cast<float*>(scratch);
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + p.ast_bytes);
+
+  // Nothing in the scratch has to start at zero: the prep kernel rewrites the whole AsT
+  // region (padding included) and every partial slot the fix-up kernel reads is written by
+  // the stream-K kernel of the same call first.
+  const int total = p.num_kb * p.mp;
+  streamk_prep_kernel<<<(total + 255) / 256, 256, 0, stream>>>(As, ast, M, p.num_kb, ld_as, p.mp);
+  st = launch_status();
+  if (st != B200FP8_OK) return st;
   StreamKArgs args;
   args.Bs = Bs;
   args.AsT = ast;

@@ -134,6 +134,41 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K);
 
 /*
+ * Decode-shape GEMM for callers that must not allocate device memory. No counterpart in the
+ * reference (there every call allocates through torch).
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - an inference server that
+ * handed all of HBM to its own pool at start-up, a real-time loop that cannot afford the
+ * device-wide synchronisation cudaMalloc/cudaFree imply, or a host layer that simply has no
+ * allocator to give this library a workspace from. b200fp8_gemm's stream-K variant needs an
+ * fp32 workspace from its caller; this entry point runs the same three kernels with the
+ * workspace in a fixed array inside the library image instead.
+ *
+ * Same arguments and result as b200fp8_gemm(..., variant = B200FP8_VARIANT_STREAMK) without
+ * the workspace pair. It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits and rules:
+ *   - the array is B200FP8_STATIC_SCRATCH_BYTES (4 MiB) per GPU that loads the library, held
+ *     until the process exits; a call whose workspace need
+ *     (b200fp8_gemm_workspace_bytes(M, N, K, B200FP8_VARIANT_STREAMK)) is larger returns
+ *     B200FP8_ERR_TOO_LARGE - once N * K is large enough to occupy all 148 SMs of a B200 that
+ *     means M <= 16 tokens (smaller problems with more tokens fit as well);
+ *     K == 0 is rejected with B200FP8_ERR_SHAPE;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array, which keeps the previous call's contents
+ *     (nothing in it needs zeroing, every word read is written earlier in the same call):
+ *     two calls whose kernels can overlap on the GPU - different streams, no dependency -
+ *     race on it. Keep calls on one stream or order them with events.
+ */
+#define B200FP8_STATIC_SCRATCH_BYTES (4u << 20)
+int b200fp8_gemm_decode_static(const void* A, const void* B, const float* As, const float* Bs, void* C,
+                               int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc,
+                               int out_dtype, uint32_t* status_word, void* stream);
+
+/*
  * Work partition of the stream-K variant, exposed for tests and tools (no counterpart
  * in the reference). `total` (weight tile, K block) units are spread over `grid` CTAs in
  * contiguous ranges: CTA c owns units [first_unit(c), first_unit(c + 1)).
