@@ -48,6 +48,16 @@ int device_info(const DeviceInfo** out) {
       auto opt_in = [&ok](const void* fn, int bytes) {
         ok = ok && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
       };
+      // setmaxnreg.inc blocks until registers are free: refuse to run a kernel whose compiled
+      // register count (what the launch allocates) cannot cover its own re-balancing plan
+      auto regs_ok = [&ok](const void* fn, int threads, int regs_needed_total) {
+        cudaFuncAttributes attr;
+        ok = ok && cudaFuncGetAttributes(&attr, fn) == cudaSuccess && attr.numRegs * threads >= regs_needed_total;
+      };
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256>), TileCfg<256>::THREADS,
+              128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_streamk_kernel<256>), StreamKCfg<256>::THREADS,
+              128 * StreamKCfg<256>::REGS_CONTROL + 256 * StreamKCfg<256>::REGS_EPILOGUE);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128>), TileCfg<128>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256>), TileCfg<256>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<16>), StreamKCfg<16>::SMEM_BYTES);
@@ -158,6 +168,12 @@ StreamKPlan streamk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
   p.ast_bytes = align_up(static_cast<int64_t>(p.num_kb) * p.mp * 4, 256);
   p.partial_bytes = 2 * p.grid * p.mp * 128 * 4;
   return p;
+}
+
+// tile variants: AsT [ceil(K/128)][M rounded up to 128] fp32
+int64_t tile_workspace_bytes(int64_t M, int64_t K) {
+  if (M == 0 || K == 0) return 0;
+  return align_up(((K + 127) / 128) * align_up(M, 128) * 4, 256);
 }
 
 double wave_efficiency(int64_t tiles, int sms) {
@@ -280,7 +296,7 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   const int sms = sm_count_or_default();
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
-  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return 0;
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return tile_workspace_bytes(M, K);
   if (variant != B200FP8_VARIANT_STREAMK) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
   if (M > 256) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
   if (M == 0 || N == 0 || K == 0) return 0;
@@ -318,7 +334,19 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
 
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) {
+    const int64_t need = tile_workspace_bytes(M, K);
+    if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
+    args.AsT = static_cast<const float*>(workspace);
+    args.m_pad = align_up(M, 128);
+    {
+      const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
+      tile_prep_kernel<<<grid, 256, 0, stream>>>(As, static_cast<float*>(workspace), M, args.m_pad,
+                                                 static_cast<int>(kblocks), ld_as);
+      st = launch_status();
+      if (st != B200FP8_OK) return st;
+    }
     args.As = As;
     args.Bs = Bs;
     args.C = C;
@@ -331,7 +359,7 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
     args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
     args.status_word = status_word;
 #ifdef B200FP8_TRACE
-    args.trace = reinterpret_cast<long long*>(workspace);  // trace builds reuse the (otherwise unused) workspace pointer
+    args.trace = reinterpret_cast<long long*>(status_word) + 1;  // trace builds: event buffer follows the status word
 #endif
     return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(A, B, args, lda, ldb, dev->sm_count, stream)
                                               : launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream);

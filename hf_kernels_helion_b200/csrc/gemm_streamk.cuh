@@ -51,6 +51,13 @@ struct StreamKCfg {
   static constexpr int EPI_COLS = MP_ / (EPI_WARPS / 4);
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   static constexpr bool REBALANCE_REGS = (EPI_COLS > 64);
+  // setmaxnreg.inc blocks until the registers exist: what the epilogue warpgroups take must
+  // fit in what the launch allocated (168 per thread at 384 threads) minus what the control
+  // warpgroup keeps.
+  static constexpr int REGS_CONTROL = 56;
+  static constexpr int REGS_EPILOGUE = 224;
+  static_assert(!REBALANCE_REGS || 128 * REGS_CONTROL + 32 * EPI_WARPS * REGS_EPILOGUE <= 168 * THREADS,
+                "setmaxnreg.inc would wait for registers that never become free");
   static constexpr int TMEM_COLS = TMEM_STAGES * MP_;  // 128, 256 or 512: a power of two >= 32
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_RING * SC_BYTES + BAR_BYTES + 1024;
@@ -138,7 +145,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint32_t* status_word = args.status_word;
 
   if (warp < 4) {
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<56>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<Cfg::REGS_CONTROL>();
   }
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -228,7 +235,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ promotion + epilogue
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<224>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     constexpr int EC = Cfg::EPI_COLS;
     const int e = warp - 4;
     const int q = warp & 3;

@@ -36,6 +36,8 @@ namespace b200fp8 {
 #endif
 
 struct GemmArgs {
+  const float* AsT;   // [ceil(K/128)][m_pad] token scales, K-block-major (written by tile_prep_kernel)
+  int64_t m_pad;      // M rounded up to 128
   const float* As;
   const float* Bs;
   void* C;
@@ -61,6 +63,15 @@ struct TileCfg {
   // registers a 384-thread CTA gets by default: the BN = 256 kernel moves registers
   // from the producer/MMA warpgroup to the two epilogue warpgroups with setmaxnreg.
   static constexpr bool REBALANCE_REGS = (BN_ == 256);
+  // setmaxnreg budget: the CTA is launched with 168 registers per thread (65536 / 384 rounded
+  // down to a multiple of 8); the control warpgroup gives registers back, the two epilogue
+  // warpgroups take them. setmaxnreg.inc BLOCKS until the registers exist, so the sum must
+  // not exceed what the launch allocated.
+  static constexpr int REGS_LAUNCH = 168;
+  static constexpr int REGS_CONTROL = 56;
+  static constexpr int REGS_EPILOGUE = 224;
+  static_assert(128 * REGS_CONTROL + 32 * EPI_WARPS * REGS_EPILOGUE <= REGS_LAUNCH * THREADS,
+                "setmaxnreg.inc would wait for registers that never become free");
   static constexpr int A_BYTES = BM * BK;
   static constexpr int B_BYTES = BN_ * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -70,6 +81,21 @@ struct TileCfg {
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
 };
+
+// Tile order: panels of kRasterGroup M-blocks; inside a panel the M index runs fastest, then
+// N. The 148 tiles in flight at any time then cover a roughly square patch of C, so the
+// A rows and B rows they share are fetched from DRAM once and hit in L2 afterwards.
+constexpr int kRasterGroup = 32;
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int per_panel = kRasterGroup * num_n;
+  const int panel = tile / per_panel;
+  const int rem = tile - panel * per_panel;
+  const int m_first = panel * kRasterGroup;
+  const int gm = (num_m - m_first) < kRasterGroup ? (num_m - m_first) : kRasterGroup;
+  n_blk = rem / gm;
+  m_blk = m_first + (rem - n_blk * gm);
+}
 
 template <int BN>
 __global__ void __launch_bounds__(TileCfg<BN>::THREADS, 1)
@@ -122,7 +148,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint32_t* status_word = args.status_word;
 
   if (warp < 4) {
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<56>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_dec<Cfg::REGS_CONTROL>();
   }
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -132,8 +158,10 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * Cfg::BM;
-        const int n0 = (tile / num_m) * BN;
+        int m_blk, n_blk;
+        tile_coords(tile, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * Cfg::BM;
+        const int n0 = n_blk * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -216,34 +244,39 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ promotion + epilogue
-    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<224>();
+    if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     const int e = warp - 4;
     const int q = warp & 3;           // TMEM lane quarter this warp may read
     const int cw = e >> 2;            // which EPI_COLS-wide column slice of the tile
     const int num_nb = static_cast<int>((N + 127) / 128);
+    constexpr int CHUNKS = Cfg::EPI_COLS / 32;
+    const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % num_m) * Cfg::BM;
-      const int n0 = (tile / num_m) * BN;
+      int m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const int m0 = m_blk * Cfg::BM;
+      const int n0 = n_blk * BN;
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
-      const int64_t row_c = row < M ? row : M - 1;
       const int col0 = n0 + cw * Cfg::EPI_COLS;
       int nb = col0 / 128;
       nb = nb < num_nb ? nb : num_nb - 1;
-      const float* as_row = args.As + row_c * args.ld_as;
+      // lanes of a warp own consecutive rows: K-block-major scales make this one coalesced
+      // 128-byte load per warp and K block (row-major As would be 32 separate sectors)
+      const float* as_col = args.AsT + row;
       const float* bs_row = args.Bs + static_cast<int64_t>(nb) * args.ld_bs;
 
-      // accumulators as 32-column groups of packed pairs: acc[g][j] = columns 32 g + 2 j, + 1
-      float2 acc[Cfg::EPI_COLS / 32][16];
+      // accumulators as 32-column groups of pairs: acc[g][j] = columns 32 g + 2 j, + 1
+      float2 acc[CHUNKS][16];
 #pragma unroll
-      for (int g = 0; g < Cfg::EPI_COLS / 32; ++g)
+      for (int g = 0; g < CHUNKS; ++g)
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[g][j] = make_float2(0.f, 0.f);
 
       // One K block: wait for its partial in TMEM, pull it into registers in 32-column
-      // chunks (the tcgen05.ld of chunk g + 1 is in flight while the FMAs of chunk g
-      // issue), hand the TMEM stage back as soon as the last chunk has landed.
+      // chunks with two tcgen05.ld in flight, hand the TMEM stage back as soon as the last
+      // chunk has landed (before its FMAs).
       auto promote = [&](float sc) -> bool {
         const uint32_t ts = it % TS;
         const uint32_t tph = (it / TS) & 1u;
@@ -254,17 +287,13 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!__all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word))) return false;
         if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 1);
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ts * BN + cw * Cfg::EPI_COLS;
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
-        // Two tcgen05.ld (32 columns each) are kept in flight; the TMEM stage is handed
-        // back as soon as the last chunk has landed in registers, before its FMAs.
+        const uint32_t taddr = tmem_base + lane_col + ts * BN;
         uint32_t pa[32], pb[32];
-        constexpr int CHUNKS = Cfg::EPI_COLS / 32;
         tmem_ld_32x32(taddr, pa);
         tmem_ld_32x32(taddr + 32, pb);
         tmem_ld_wait_32(pa);
         tmem_ld_wait_32(pb);
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
 #pragma unroll
         for (int g = 0; g < CHUNKS; g += 2) {
           const bool more = g + 2 < CHUNKS;
@@ -272,10 +301,9 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[ts]);
-            if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
+            if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
           }
           fma32_scalar(acc[g], pa, sc);
-          if (g == 0 && tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 5);
           if (more) tmem_ld_32x32(taddr + (g + 2) * 32, pa);
           fma32_scalar(acc[g + 1], pb, sc);
           if (more) {
@@ -283,13 +311,12 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tmem_ld_wait_32(pa);
             tmem_ld_wait_32(pb);
           }
-          if (g == 0 && tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 6);
         }
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 7);
+        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
         return true;
       };
 
-      // The scales As[row, kb] and Bs[nb, kb] come from global memory (L2 latency of several
+      // The scales AsT[kb][row] and Bs[nb, kb] come from global memory (L2 latency of several
       // hundred clocks). They are fetched a whole group of PF K blocks ahead so that their
       // first use never stalls the promotion loop.
       constexpr int PF = 4;
@@ -297,7 +324,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
       for (int j = 0; j < PF; ++j) {
         const int k = j < num_kb ? j : num_kb - 1;
-        sa_c[j] = __ldg(as_row + k);
+        sa_c[j] = __ldg(as_col + k * args.m_pad);
         sb_c[j] = __ldg(bs_row + k);
       }
       for (int kb0 = 0; ok && kb0 < num_kb; kb0 += PF) {
@@ -305,7 +332,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int j = 0; j < PF; ++j) {
           int k = kb0 + PF + j;
           k = k < num_kb ? k : num_kb - 1;
-          sa_n[j] = __ldg(as_row + k);
+          sa_n[j] = __ldg(as_col + k * args.m_pad);
           sb_n[j] = __ldg(bs_row + k);
         }
 #pragma unroll
@@ -367,6 +394,30 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// AsT[kb][m] = As[m][kb] for m < M, 0 for M <= m < m_pad: 32 x 32 tiles through shared
+// memory so that both the row-major reads and the K-block-major writes are coalesced.
+__global__ void __launch_bounds__(256)
+tile_prep_kernel(const float* __restrict__ As, float* __restrict__ AsT, int64_t M, int64_t m_pad, int num_kb,
+                 int64_t ld_as) {
+  __shared__ float t[32][33];
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int kb0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int64_t m = m0 + ty + i;
+    const int kb = kb0 + tx;
+    t[ty + i][tx] = (m < M && kb < num_kb) ? __ldg(As + m * ld_as + kb) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int kb = kb0 + ty + i;
+    const int64_t m = m0 + tx;
+    if (kb < num_kb && m < m_pad) AsT[static_cast<int64_t>(kb) * m_pad + m] = t[tx][ty + i];
   }
 }
 

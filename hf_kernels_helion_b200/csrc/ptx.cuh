@@ -108,6 +108,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Non-blocking probe of a phase (mbarrier.test_wait). Issued early, its shared-memory round
+// trip overlaps whatever independent work follows; mbar_wait_probed finishes the job.
+__device__ __forceinline__ bool mbar_probe(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits that tolerate failure: used by the promotion warps, which after a timeout keep
+// running (every later wait returns at once because the abort flag is up) so that the warp
+// stays converged for its .sync.aligned instructions and the CTA still reaches its teardown;
+// the output is then invalid and the status word says so.
+__device__ __forceinline__ void mbar_wait_probed(bool probed_ready, uint64_t* bar, uint32_t parity,
+                                                 volatile uint32_t* abort_flag, uint32_t* status_word) {
+  if (!probed_ready && *abort_flag == 0u) (void)mbar_wait(bar, parity, abort_flag, status_word);
+}
+
 // Warp-wide wait: lane 0 polls, the result is broadcast (one mbarrier transaction per
 // poll instead of 32). Must be called by all 32 lanes.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
@@ -258,12 +283,14 @@ __device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
       : "memory");
 }
 
-// acc[0..31] += p[0..31] * s with packed two-wide fp32 FMAs (fma.rn.f32x2, sm_100).
+// acc[0..31] += p[0..31] * s (acc kept as pairs of adjacent columns).
 __device__ __forceinline__ void fma32_scalar(float2 (&acc)[16], const uint32_t (&p)[32], float s) {
-  const float2 s2 = make_float2(s, s);
+  // plain FFMA: measured faster here than fma.rn.f32x2 (3 issue clocks per packed pair)
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
-    acc[j] = __ffma2_rn(make_float2(__uint_as_float(p[2 * j]), __uint_as_float(p[2 * j + 1])), s2, acc[j]);
+  for (int j = 0; j < 16; ++j) {
+    acc[j].x = fmaf(__uint_as_float(p[2 * j]), s, acc[j].x);
+    acc[j].y = fmaf(__uint_as_float(p[2 * j + 1]), s, acc[j].y);
+  }
 }
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {

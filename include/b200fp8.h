@@ -53,7 +53,7 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_AUTO 0    /* pick by shape */
 #define B200FP8_VARIANT_TILE128 1 /* persistent tcgen05 kernel, 128x128 output tiles */
 #define B200FP8_VARIANT_TILE256 2 /* persistent tcgen05 kernel, 128x256 output tiles */
-#define B200FP8_VARIANT_STREAMK 3 /* swap-AB stream-K kernel for M <= 256 (decode shapes), needs workspace */
+#define B200FP8_VARIANT_STREAMK 3 /* swap-AB stream-K kernel for M <= 256 (decode shapes) */
 
 /* codes a kernel may leave in *status_word */
 #define B200FP8_DEV_OK 0u
@@ -116,9 +116,10 @@ int b200fp8_quant_weight(const void* w, void* q, float* s,
  * M, N, K otherwise arbitrary (ragged edges are masked). M == 0 or N == 0 is a
  * no-op; K == 0 writes zeros.
  *
- * `workspace` is only used by B200FP8_VARIANT_STREAMK (and by AUTO when it picks
- * that variant); size it with b200fp8_gemm_workspace_bytes for the same
- * (M, N, K, variant). Its contents need no initialisation.
+ * `workspace` holds per-call scratch (a K-block-major copy of As for every variant, plus
+ * the fp32 partial tiles of B200FP8_VARIANT_STREAMK); size it with
+ * b200fp8_gemm_workspace_bytes for the same (M, N, K, variant), align it to 256 bytes. Its
+ * contents need no initialisation.
  */
 int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs, void* C,
                  int64_t M, int64_t N, int64_t K,

@@ -71,9 +71,11 @@ def test_argument_errors_need_no_device(lib):
 
 def test_workspace_and_variant_queries(lib):
     AUTO, T128, T256, SK = 0, 1, 2, 3
-    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T128) == 0
-    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T256) == 0
-    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, AUTO) == 0
+    ast = 64 * 4096 * 4                                       # K-block-major copy of As: [K/128][M] fp32
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T128) == ast
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T256) == ast
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, AUTO) == ast
+    assert lib.b200fp8_gemm_workspace_bytes(300, 512, 200, T128) == 2 * 384 * 4   # M padded to 128, K blocks rounded up
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, SK) == -5     # M > 256 cannot use stream-K
     assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, 42) == -5
     assert lib.b200fp8_gemm_workspace_bytes(-1, 1, 1, AUTO) == -2
