@@ -176,6 +176,29 @@ int64_t tile_workspace_bytes(int64_t M, int64_t K) {
   return align_up(((K + 127) / 128) * align_up(M, 128) * 4, 256);
 }
 
+// tile stream-K (128x256 tiles, M <= 256): groups of num_m CTAs share the (N tile, K block) units
+struct TileSkPlan {
+  int num_m, num_n, num_kb;
+  int groups;             // 0 when the shape cannot use this mode
+  int64_t grid;
+  int64_t ast_bytes, partial_bytes;
+};
+
+TileSkPlan tile_sk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+  TileSkPlan p;
+  p.num_m = static_cast<int>((M + 127) / 128);
+  p.num_n = static_cast<int>((N + 255) / 256);
+  p.num_kb = static_cast<int>((K + 127) / 128);
+  const int64_t total = static_cast<int64_t>(p.num_n) * p.num_kb;
+  int64_t groups = p.num_m > 0 ? sm_count / p.num_m : 0;
+  if (groups > total) groups = total;
+  p.groups = (M > 256 || groups < 1) ? 0 : static_cast<int>(groups);
+  p.grid = static_cast<int64_t>(p.groups) * p.num_m;
+  p.ast_bytes = tile_workspace_bytes(M, K);
+  p.partial_bytes = 2 * p.grid * 128 * 256 * 4;
+  return p;
+}
+
 double wave_efficiency(int64_t tiles, int sms) {
   if (tiles <= 0) return 1.0;
   const int64_t waves = (tiles + sms - 1) / sms;
@@ -183,8 +206,11 @@ double wave_efficiency(int64_t tiles, int sms) {
 }
 
 int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
-  (void)K;
-  if (M <= 256) return B200FP8_VARIANT_STREAMK;
+  // Decode shapes (M <= 256) are weight-streaming and HBM-bound. Measured on B200 at N = 28672,
+  // K = 8192: the plain 128x256 tile kernel (46 us at M = 16, 5.1 TB/s with 112 of 148 SMs busy)
+  // beats both stream-K forms (swap-AB 65 us; K-split tiles 58 us including their fix-up pass),
+  // so AUTO never picks those; they stay selectable by name.
+  if (M <= 256) return (N > 128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
   const int64_t num_m = (M + 127) / 128;
   const double e128 = wave_efficiency(num_m * ((N + 127) / 128), sm_count);
   const double e256 = wave_efficiency(num_m * ((N + 255) / 256), sm_count);
@@ -194,14 +220,14 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
 
 template <int BN>
 int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb, int sm_count,
-                cudaStream_t stream) {
+                cudaStream_t stream, int64_t sk_grid = 0) {
   CUtensorMap ta, tb;
   int st = make_tmap_u8(&ta, A, args.M, args.K, lda, 128);
   if (st != B200FP8_OK) return st;
   st = make_tmap_u8(&tb, B, args.N, args.K, ldb, BN);
   if (st != B200FP8_OK) return st;
   const int64_t tiles = ((args.M + 127) / 128) * ((args.N + BN - 1) / BN);
-  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  const int grid = sk_grid > 0 ? static_cast<int>(sk_grid) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
   gemm_tile_kernel<BN><<<grid, TileCfg<BN>::THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, args);
   return launch_status();
 }
@@ -297,6 +323,12 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
   const int sms = sm_count_or_default();
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return tile_workspace_bytes(M, K);
+  if (variant == B200FP8_VARIANT_TILE256_SK) {
+    if (M > 256) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
+    if (M == 0 || N == 0 || K == 0) return 0;
+    const TileSkPlan p = tile_sk_plan(M, N, K, sms);
+    return p.ast_bytes + p.partial_bytes;
+  }
   if (variant != B200FP8_VARIANT_STREAMK) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
   if (M > 256) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
   if (M == 0 || N == 0 || K == 0) return 0;
@@ -310,7 +342,7 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
   if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
-  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_STREAMK) return B200FP8_ERR_VARIANT;
+  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_TILE256_SK) return B200FP8_ERR_VARIANT;
   if (M == 0 || N == 0) return B200FP8_OK;
   if (C == nullptr) return B200FP8_ERR_NULL;
   if (ldc < N) return B200FP8_ERR_SHAPE;
@@ -333,11 +365,54 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
 
+  if (variant == B200FP8_VARIANT_TILE256_SK) {
+    if (M > 256) return B200FP8_ERR_VARIANT;
+    const TileSkPlan p = tile_sk_plan(M, N, K, dev->sm_count);
+    if (p.groups < 1) return B200FP8_ERR_VARIANT;
+    if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < p.ast_bytes + p.partial_bytes)
+      return B200FP8_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
+    GemmArgs args;
+    args.sk_groups = p.groups;
+    args.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + p.ast_bytes);
+    args.AsT = static_cast<const float*>(workspace);
+    args.m_pad = align_up(M, 128);
+    {
+      const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
+      tile_prep_kernel<<<grid, 256, 0, stream>>>(As, static_cast<float*>(workspace), M, args.m_pad,
+                                                 static_cast<int>(kblocks), ld_as);
+      st = launch_status();
+      if (st != B200FP8_OK) return st;
+    }
+    args.As = As;
+    args.Bs = Bs;
+    args.C = C;
+    args.M = M;
+    args.N = N;
+    args.K = K;
+    args.ld_as = ld_as;
+    args.ld_bs = ld_bs;
+    args.ldc = ldc;
+    args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
+    args.status_word = status_word;
+#ifdef B200FP8_TRACE
+    args.trace = nullptr;
+#endif
+    st = launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream, p.grid);
+    if (st != B200FP8_OK) return st;
+    const dim3 fix_grid(static_cast<unsigned>(p.num_n * p.num_m), 16u);
+    tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, p.num_kb, ldc,
+                                                       out_dtype == B200FP8_OUT_FP32, 256, p.num_m, p.num_n, p.groups);
+    return launch_status();
+  }
+
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) {
     const int64_t need = tile_workspace_bytes(M, K);
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
+    args.sk_groups = 0;
+    args.partial = nullptr;
     args.AsT = static_cast<const float*>(workspace);
     args.m_pad = align_up(M, 128);
     {

@@ -63,15 +63,6 @@ struct StreamKCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_RING * SC_BYTES + BAR_BYTES + 1024;
 };
 
-// First unit of CTA c when `total` units are spread over `grid` CTAs.
-__host__ __device__ __forceinline__ int64_t streamk_first_unit(int64_t c, int64_t total, int64_t grid) {
-  return (c * total) / grid;
-}
-// The CTA that owns unit u.
-__host__ __device__ __forceinline__ int64_t streamk_owner(int64_t u, int64_t total, int64_t grid) {
-  return ((u + 1) * grid - 1) / total;
-}
-
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -35,7 +35,24 @@ namespace b200fp8 {
 #define B200FP8_TRACE_EVENT(role, idx, tag) do { } while (0)
 #endif
 
+// Even split of `total` work units over `grid` owners in contiguous ranges: owner c has
+// units [streamk_first_unit(c), streamk_first_unit(c + 1)).
+__host__ __device__ __forceinline__ int64_t streamk_first_unit(int64_t c, int64_t total, int64_t grid) {
+  return (c * total) / grid;
+}
+__host__ __device__ __forceinline__ int64_t streamk_owner(int64_t u, int64_t total, int64_t grid) {
+  return ((u + 1) * grid - 1) / total;
+}
+
 struct GemmArgs {
+  // Stream-K mode (sk_groups > 0, used when M spans at most a few 128-row blocks): the
+  // (N tile, K block) units are split evenly over sk_groups groups of num_m CTAs; CTA c
+  // works on M block c % num_m of group c / num_m, so that the CTAs of a group stream the
+  // same weight tiles at the same time and every SM gets the same share of the weight.
+  // Segments that do not cover a whole K range go to `partial` as fp32 [slot][128][BN],
+  // slot = 2 * cta + (0 for the CTA's first segment, 1 for a later one).
+  int sk_groups;
+  float* partial;
   const float* AsT;   // [ceil(K/128)][m_pad] token scales, K-block-major (written by tile_prep_kernel)
   int64_t m_pad;      // M rounded up to 128
   const float* As;
@@ -95,6 +112,62 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   const int gm = (num_m - m_first) < kRasterGroup ? (num_m - m_first) : kRasterGroup;
   n_blk = rem / gm;
   m_blk = m_first + (rem - n_blk * gm);
+}
+
+// One CTA's work as a sequence of segments = (output tile, K-block range).
+struct Segment {
+  int m_blk, n_blk, kb_begin, kb_end;
+  bool first;   // first segment of this CTA
+};
+
+struct SegCursor {
+  int tile;         // tile mode: next tile index
+  int64_t u, u1;    // stream-K mode: remaining units [u, u1) of this CTA's group
+  bool started;
+};
+
+__device__ __forceinline__ SegCursor seg_begin(int sk_groups, int num_m, int num_n, int num_kb) {
+  SegCursor c;
+  c.tile = static_cast<int>(blockIdx.x);
+  c.started = false;
+  c.u = c.u1 = 0;
+  if (sk_groups > 0) {
+    const int64_t total = static_cast<int64_t>(num_n) * num_kb;
+    const int64_t g = blockIdx.x / num_m;
+    c.u = streamk_first_unit(g, total, sk_groups);
+    c.u1 = streamk_first_unit(g + 1, total, sk_groups);
+  }
+  return c;
+}
+
+// Number of K blocks this CTA processes in total.
+__device__ __forceinline__ uint32_t seg_total_kblocks(const SegCursor& c, int sk_groups, int num_tiles, int num_kb) {
+  if (sk_groups > 0) return static_cast<uint32_t>(c.u1 - c.u);
+  const int mine = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                   static_cast<int>(gridDim.x);
+  return static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
+}
+
+__device__ __forceinline__ bool seg_next(SegCursor& c, int sk_groups, int num_m, int num_n, int num_kb, int num_tiles,
+                                         Segment& s) {
+  s.first = !c.started;
+  c.started = true;
+  if (sk_groups > 0) {
+    if (c.u >= c.u1) return false;
+    s.m_blk = static_cast<int>(blockIdx.x % num_m);
+    s.n_blk = static_cast<int>(c.u / num_kb);
+    s.kb_begin = static_cast<int>(c.u - static_cast<int64_t>(s.n_blk) * num_kb);
+    const int64_t left = c.u1 - c.u;
+    s.kb_end = (num_kb - s.kb_begin) < left ? num_kb : s.kb_begin + static_cast<int>(left);
+    c.u += s.kb_end - s.kb_begin;
+    return true;
+  }
+  if (c.tile >= num_tiles) return false;
+  tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
+  s.kb_begin = 0;
+  s.kb_end = num_kb;
+  c.tile += static_cast<int>(gridDim.x);
+  return true;
 }
 
 template <int BN>
@@ -157,12 +230,12 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       prefetch_tmap(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(tile, num_m, num_n, m_blk, n_blk);
-        const int m0 = m_blk * Cfg::BM;
-        const int n0 = n_blk * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      SegCursor cur = seg_begin(args.sk_groups, num_m, num_n, num_kb);
+      Segment seg;
+      while (ok && seg_next(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+        const int m0 = seg.m_blk * Cfg::BM;
+        const int n0 = seg.n_blk * BN;
+        for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           B200FP8_TRACE_EVENT(0, it, 0);
@@ -201,8 +274,10 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t it = 0;
     uint32_t last = 0xffffffffu;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+    const SegCursor cur0 = seg_begin(args.sk_groups, num_m, num_n, num_kb);
+    const uint32_t total_it = seg_total_kblocks(cur0, args.sk_groups, num_tiles, num_kb);
+    {
+      for (; it < total_it; ++it) {
         if ((it & 1u) != p) continue;
         const uint32_t s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
@@ -253,11 +328,11 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      int m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
-      const int m0 = m_blk * Cfg::BM;
-      const int n0 = n_blk * BN;
+    SegCursor cur = seg_begin(args.sk_groups, num_m, num_n, num_kb);
+    Segment seg;
+    while (ok && seg_next(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+      const int m0 = seg.m_blk * Cfg::BM;
+      const int n0 = seg.n_blk * BN;
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
       const int col0 = n0 + cw * Cfg::EPI_COLS;
       int nb = col0 / 128;
@@ -321,23 +396,24 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // first use never stalls the promotion loop.
       constexpr int PF = 4;
       float sa_c[PF], sb_c[PF], sa_n[PF], sb_n[PF];
+      const int kb_last = seg.kb_end - 1;
 #pragma unroll
       for (int j = 0; j < PF; ++j) {
-        const int k = j < num_kb ? j : num_kb - 1;
+        const int k = seg.kb_begin + j < seg.kb_end ? seg.kb_begin + j : kb_last;
         sa_c[j] = __ldg(as_col + k * args.m_pad);
         sb_c[j] = __ldg(bs_row + k);
       }
-      for (int kb0 = 0; ok && kb0 < num_kb; kb0 += PF) {
+      for (int kb0 = seg.kb_begin; ok && kb0 < seg.kb_end; kb0 += PF) {
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
           int k = kb0 + PF + j;
-          k = k < num_kb ? k : num_kb - 1;
+          k = k < seg.kb_end ? k : kb_last;
           sa_n[j] = __ldg(as_col + k * args.m_pad);
           sb_n[j] = __ldg(bs_row + k);
         }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
-          if (ok && kb0 + j < num_kb) ok = promote(sa_c[j] * sb_c[j]);
+          if (ok && kb0 + j < seg.kb_end) ok = promote(sa_c[j] * sb_c[j]);
         }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
@@ -348,6 +424,17 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!ok) break;
 
 #define ACC(i) (((i) & 1) ? acc[(i) >> 5][((i) & 31) >> 1].y : acc[(i) >> 5][((i) & 31) >> 1].x)
+      if (seg.kb_begin != 0 || seg.kb_end != num_kb) {
+        // stream-K: this CTA saw only part of the K range - leave the fp32 partial sums of the
+        // rows that exist in the workspace; tile_sk_fixup_kernel adds the pieces of the tile
+        if (row < M) {
+          const int64_t slot = 2 * static_cast<int64_t>(blockIdx.x) + (seg.first ? 0 : 1);
+          float* prow = args.partial + (slot * Cfg::BM + (q * 32 + lane)) * BN + cw * Cfg::EPI_COLS;
+#pragma unroll
+          for (int j = 0; j < Cfg::EPI_COLS; j += 4)
+            *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
+        }
+      } else
       if (row < M && col0 < N) {
         if (args.out_fp32) {
           float* crow = reinterpret_cast<float*>(args.C) + row * args.ldc + col0;
@@ -394,6 +481,46 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// Stream-K mode: adds the fp32 pieces of every output tile whose K range was split between
+// groups, in ascending group order (fixed order: bit-reproducible), and writes C. Grid =
+// (num_n * num_m tiles, 16 row chunks of 8 rows); BN threads, one per tile column. Tiles
+// that one CTA covered completely were written by the GEMM kernel and are skipped.
+__global__ void __launch_bounds__(256)
+tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
+                     int out_fp32, int BN, int num_m, int num_n, int sk_groups) {
+  const int n_blk = blockIdx.x / num_m;
+  const int m_blk = blockIdx.x - n_blk * num_m;
+  const int64_t total = static_cast<int64_t>(num_n) * num_kb;
+  const int64_t g_first = streamk_owner(static_cast<int64_t>(n_blk) * num_kb, total, sk_groups);
+  const int64_t g_last = streamk_owner(static_cast<int64_t>(n_blk) * num_kb + num_kb - 1, total, sk_groups);
+  if (g_first == g_last) return;
+  const int64_t col = static_cast<int64_t>(n_blk) * BN + threadIdx.x;
+  if (static_cast<int>(threadIdx.x) >= BN || col >= N) return;
+  const int r0 = blockIdx.y * 8;
+  float sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+  for (int64_t g = g_first; g <= g_last; ++g) {
+    const int64_t cta = g * num_m + m_blk;
+    const int64_t first_tile_of_g = streamk_first_unit(g, total, sk_groups) / num_kb;
+    const int64_t slot = 2 * cta + (first_tile_of_g == n_blk ? 0 : 1);
+    const float* src = partial + (slot * 128 + r0) * BN + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (static_cast<int64_t>(m_blk) * 128 + r0 + i < M) sum[i] += __ldg(src + static_cast<int64_t>(i) * BN);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t row = static_cast<int64_t>(m_blk) * 128 + r0 + i;
+    if (row < M) {
+      if (out_fp32)
+        reinterpret_cast<float*>(C)[row * ldc + col] = sum[i];
+      else
+        reinterpret_cast<__nv_bfloat16*>(C)[row * ldc + col] = __float2bfloat16_rn(sum[i]);
+    }
   }
 }
 

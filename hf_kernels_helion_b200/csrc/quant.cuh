@@ -21,41 +21,79 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
   return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
 }
 
+// max |x| over 8 bf16 (one uint4), as fp32; packed bf16x2 abs / max, exact.
 __device__ __forceinline__ float amax8(const uint4& v) {
-  float m = fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x)));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y))));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w))));
-  return m;
+  const uint32_t m = 0x7FFF7FFFu;
+  uint32_t a = v.x & m, b = v.y & m, c = v.z & m, d = v.w & m;
+  __nv_bfloat162 ab = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  __nv_bfloat162 cd = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&c), *reinterpret_cast<__nv_bfloat162*>(&d));
+  ab = __hmax2(ab, cd);
+  const uint32_t w = *reinterpret_cast<uint32_t*>(&ab);
+  return fmaxf(bf16_lo(w), bf16_hi(w));
 }
 
-// x / scale for the e4m3 cast, bit-identical to e4m3_rne(__fdiv_rn(x, scale)) but without
-// a division per element. q = x * rcp (rcp = 1 / scale, correctly rounded) is within
-// 2 ulp of the IEEE quotient; the cast to e4m3 can only differ if a rounding boundary
-// of e4m3 lies between the two, i.e. if q sits within a few ulp of a tie (fp32
-// mantissa bits below the three kept ones equal to 0x80000). Those rare elements, the
-// e4m3 subnormal range (different tie positions) and non-finite / out-of-range q take
-// the exact division instead.
-__device__ __forceinline__ float quotient_for_cast(float x, float scale, float rcp) {
-  const float q = x * rcp;
-  const uint32_t mag = __float_as_uint(q) & 0x7FFFFFFFu;
-  const bool near_tie = ((mag & 0xFFFFFu) - (0x80000u - 8u)) <= 16u;
-  const bool odd_range = mag >= 0x43E80000u /* 464, inf, NaN */ || mag < 0x3C800000u /* 2^-6 */;
-  if ((near_tie || odd_range) && mag != 0u) return __fdiv_rn(x, scale);  // a zero product casts to the same zero
-  return q;
-}
+// e4m3(x / scale) without a division per element, bit-identical to the division.
+// q = x * rcp (rcp = 1 / scale, correctly rounded) is within 2 ulp of the IEEE quotient, so
+// the e4m3 cast of the two can differ only if an e4m3 rounding boundary lies between them:
+//   - q within a few ulp of a tie of the normal e4m3 range, i.e. the 20 fp32 mantissa bits
+//     below the three kept ones are about 0x80000;
+//   - 0 < |q| < 2^-6 (the e4m3 subnormal range has its ties elsewhere).
+// Both conditions are folded into two running unsigned minima over the elements a thread
+// converts; if either fires (rare), the thread redoes its elements with the true division.
+// (|q| cannot leave the range upwards since |x| <= amax; a scale so small that 1 / scale
+// overflows is sent to the division path as a whole.)
+struct ExactnessProbe {
+  uint32_t tie_min = 0xFFFFFFFFu;   // min over elements of (bits & 0xFFFFF) - (0x80000 - 8); <= 16 means "near a tie"
+  uint32_t low_min = 0xFFFFFFFFu;   // min over elements of |q| bits - 1; < 0x3C800000 - 1 means "0 < |q| < 2^-6"
+  __device__ __forceinline__ float mul(float x, float rcp) {
+    const float q = x * rcp;
+    const uint32_t bits = __float_as_uint(q);
+    tie_min = min(tie_min, (bits & 0xFFFFFu) - (0x80000u - 8u));
+    low_min = min(low_min, (bits & 0x7FFFFFFFu) - 1u);
+    return q;
+  }
+  __device__ __forceinline__ bool inexact() const { return tie_min <= 16u || low_min < 0x3C800000u - 1u; }
+};
 
-// 8 bf16 (one uint4) divided by `scale` and packed into 8 e4m3 bytes (one uint2).
-// scale == 0 (all-zero group) yields zero bytes instead of the 0/0 NaN of the formula.
-__device__ __forceinline__ uint2 quant8(const uint4& v, float scale) {
-  if (scale == 0.f) return make_uint2(0u, 0u);
-  const float rcp = __frcp_rn(scale);
+__device__ __forceinline__ uint2 quant8_fast(const uint4& v, float rcp, ExactnessProbe& pr) {
   uint2 o;
-  o.x = cvt_e4m3x2(quotient_for_cast(bf16_lo(v.x), scale, rcp), quotient_for_cast(bf16_hi(v.x), scale, rcp)) |
-        (cvt_e4m3x2(quotient_for_cast(bf16_lo(v.y), scale, rcp), quotient_for_cast(bf16_hi(v.y), scale, rcp)) << 16);
-  o.y = cvt_e4m3x2(quotient_for_cast(bf16_lo(v.z), scale, rcp), quotient_for_cast(bf16_hi(v.z), scale, rcp)) |
-        (cvt_e4m3x2(quotient_for_cast(bf16_lo(v.w), scale, rcp), quotient_for_cast(bf16_hi(v.w), scale, rcp)) << 16);
+  o.x = cvt_e4m3x2(pr.mul(bf16_lo(v.x), rcp), pr.mul(bf16_hi(v.x), rcp)) |
+        (cvt_e4m3x2(pr.mul(bf16_lo(v.y), rcp), pr.mul(bf16_hi(v.y), rcp)) << 16);
+  o.y = cvt_e4m3x2(pr.mul(bf16_lo(v.z), rcp), pr.mul(bf16_hi(v.z), rcp)) |
+        (cvt_e4m3x2(pr.mul(bf16_lo(v.w), rcp), pr.mul(bf16_hi(v.w), rcp)) << 16);
   return o;
+}
+
+__device__ __forceinline__ uint2 quant8_div(const uint4& v, float scale) {
+  uint2 o;
+  o.x = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.x), scale), __fdiv_rn(bf16_hi(v.x), scale)) |
+        (cvt_e4m3x2(__fdiv_rn(bf16_lo(v.y), scale), __fdiv_rn(bf16_hi(v.y), scale)) << 16);
+  o.y = cvt_e4m3x2(__fdiv_rn(bf16_lo(v.z), scale), __fdiv_rn(bf16_hi(v.z), scale)) |
+        (cvt_e4m3x2(__fdiv_rn(bf16_lo(v.w), scale), __fdiv_rn(bf16_hi(v.w), scale)) << 16);
+  return o;
+}
+
+// N x 8 bf16 (N uint4) divided by `scale` and packed into N x 8 e4m3 bytes (N uint2).
+// scale == 0 (all-zero group) yields zero bytes instead of the 0/0 NaN of the formula.
+template <int NV>
+__device__ __forceinline__ void quant_vecs(const uint4 (&v)[NV], float scale, uint2 (&o)[NV]) {
+  if (scale == 0.f) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i] = make_uint2(0u, 0u);
+    return;
+  }
+  bool exact_path = scale < 1.0e-30f;   // 1 / scale would overflow or lose bits: divide
+  if (!exact_path) {
+    const float rcp = __frcp_rn(scale);
+    ExactnessProbe pr;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i] = quant8_fast(v[i], rcp, pr);
+    exact_path = pr.inexact();
+  }
+  if (exact_path) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i] = quant8_div(v[i], scale);
+  }
 }
 
 // Eight consecutive threads own one 128-element group: each loads two 16-byte
@@ -70,36 +108,55 @@ quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, f
   const int64_t groups_per_pass = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 3;
   // total_groups rounded up to a multiple of 4 keeps all 32 lanes of a warp inside the shuffle
   const int64_t padded_groups = (total_groups + 3) & ~int64_t(3);
-  for (int64_t g = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 3; g < padded_groups;
-       g += groups_per_pass) {
-    const bool live = g < total_groups;
-    const int64_t row = live ? g / groups_per_row : 0;
-    const int64_t kg = live ? g - row * groups_per_row : 0;
-    const int64_t col = kg * 128 + sub * 16;
-    const bool has0 = live && (col + 8 <= K);
-    const bool has1 = live && (col + 16 <= K);
-    uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = make_uint4(0u, 0u, 0u, 0u);
-    const __nv_bfloat16* src = x + row * ldx + col;
-    if (has0) v0 = __ldg(reinterpret_cast<const uint4*>(src));
-    if (has1) v1 = __ldg(reinterpret_cast<const uint4*>(src + 8));
-    float amax = fmaxf(amax8(v0), amax8(v1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-    const float scale = __fdiv_rn(amax, 448.0f);
-    uint8_t* dst = q + row * ldq + col;
-    if (has1) {
-      const uint2 a = quant8(v0, scale), b = quant8(v1, scale);
-      if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(a.x, a.y, b.x, b.y);
-      } else {
-        *reinterpret_cast<uint2*>(dst) = a;
-        *reinterpret_cast<uint2*>(dst + 8) = b;
-      }
-    } else if (has0) {
-      *reinterpret_cast<uint2*>(dst) = quant8(v0, scale);
+
+  // reduced, and the two dependent chains (shuffles, division, reciprocal) interleave.
+  constexpr int U = 1;
+  for (int64_t g0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 3; g0 < padded_groups;
+       g0 += U * groups_per_pass) {
+    uint4 v[U][2];
+    int64_t row[U], kg[U], col[U];
+    bool live[U], has0[U], has1[U], in_loop[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t g = g0 + u * groups_per_pass;
+      in_loop[u] = g < padded_groups;          // warp-uniform: whole warps share a group quadruple
+      live[u] = g < total_groups;
+      row[u] = live[u] ? g / groups_per_row : 0;
+      kg[u] = live[u] ? g - row[u] * groups_per_row : 0;
+      col[u] = kg[u] * 128 + sub * 16;
+      has0[u] = live[u] && (col[u] + 8 <= K);
+      has1[u] = live[u] && (col[u] + 16 <= K);
+      v[u][0] = make_uint4(0u, 0u, 0u, 0u);
+      v[u][1] = make_uint4(0u, 0u, 0u, 0u);
+      const __nv_bfloat16* src = x + row[u] * ldx + col[u];
+      if (has0[u]) v[u][0] = __ldg(reinterpret_cast<const uint4*>(src));
+      if (has1[u]) v[u][1] = __ldg(reinterpret_cast<const uint4*>(src + 8));
     }
-    if (live && sub == 0) s[row * lds + kg] = scale;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!in_loop[u]) continue;
+      float amax = fmaxf(amax8(v[u][0]), amax8(v[u][1]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const float scale = __fdiv_rn(amax, 448.0f);
+      uint8_t* dst = q + row[u] * ldq + col[u];
+      if (has0[u]) {
+        uint2 o[2];   // a missing second vector is zeros and is simply not stored
+        quant_vecs<2>(v[u], scale, o);
+        if (has1[u]) {
+          if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
+          } else {
+            *reinterpret_cast<uint2*>(dst) = o[0];
+            *reinterpret_cast<uint2*>(dst + 8) = o[1];
+          }
+        } else {
+          *reinterpret_cast<uint2*>(dst) = o[0];
+        }
+      }
+      if (live[u] && sub == 0) s[row[u] * lds + kg[u]] = scale;
+    }
   }
 }
 
@@ -130,10 +187,11 @@ quant_weight_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
   const float scale = __fdiv_rn(amax, 448.0f);
+  uint2 o[8];
+  quant_vecs<8>(v, scale, o);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    if (row < N && col0 + i * 8 + 8 <= K)
-      *reinterpret_cast<uint2*>(q + row * ldq + col0 + i * 8) = quant8(v[i], scale);
+    if (row < N && col0 + i * 8 + 8 <= K) *reinterpret_cast<uint2*>(q + row * ldq + col0 + i * 8) = o[i];
   }
   if (threadIdx.x == 0) s[nb * lds + kb] = scale;
 }

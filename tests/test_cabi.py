@@ -85,8 +85,13 @@ def test_workspace_and_variant_queries(lib):
     assert 0 < w1 == w16 < w256
     grid = lib.b200fp8_streamk_grid(16, 28672, 8192)
     assert w16 == 64 * 16 * 4 + 2 * grid * 16 * 128 * 4      # AsT [K/128][16] + two partial slots per CTA
-    assert lib.b200fp8_gemm_pick_variant(1, 28672, 8192) == SK
-    assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == SK
+    TSK = 4
+    assert lib.b200fp8_gemm_pick_variant(1, 28672, 8192) == T256     # decode shapes: plain tile kernel measured fastest
+    assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == T256
+    assert lib.b200fp8_gemm_pick_variant(16, 128, 512) == T128
+    assert lib.b200fp8_gemm_workspace_bytes(300, 28672, 8192, TSK) == -5     # M > 256
+    g = 148 // 1
+    assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4 + 2 * g * 128 * 256 * 4
     assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256)
 
 

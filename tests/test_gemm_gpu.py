@@ -38,7 +38,7 @@ def _run(device, A, B, As, Bs, dtype, variant):
     return out.cpu()
 
 
-@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "auto"])
+@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk", "auto"])
 @pytest.mark.parametrize("name", ["small_96x256x384", "small_130x128x256", "small_1x384x512"])
 def test_golden_vectors_from_reference_source(device, name, variant):
     z = np.load(GOLDEN / f"{name}.npz")
@@ -104,9 +104,13 @@ def test_streamk_vs_oracle(device, M, N, K):
     assert oracle.max_err_over_rms(out32, ref) <= FP32_TOL
     out16 = _run(device, A, B, As, Bs, torch.bfloat16, "streamk")
     assert oracle.bf16_ulp_error(out16, ref) <= 1
-    # all three kernels agree with each other to fp32 rounding
+    # all kernels agree with each other to fp32 rounding
     alt = _run(device, A, B, As, Bs, torch.float32, "tile128")
     assert oracle.max_err_over_rms(out32, alt) <= FP32_TOL
+    sk32 = _run(device, A, B, As, Bs, torch.float32, "tile256_sk")
+    assert oracle.max_err_over_rms(sk32, ref) <= FP32_TOL
+    sk16 = _run(device, A, B, As, Bs, torch.bfloat16, "tile256_sk")
+    assert oracle.bf16_ulp_error(sk16, ref) <= 1
 
 
 @pytest.mark.parametrize("M", [1, 16, 64, 256])
@@ -116,8 +120,12 @@ def test_decode_shapes_full_size(device, M):
     N, K = 28672, 8192
     A, B, As, Bs = oracle.make_quantised_inputs(M, N, K, 0)
     dA, dB, dAs, dBs = _dev((A, B, As, Bs), device)
+    for v in ("streamk", "tile256_sk"):          # the two stream-K forms at full size, against AUTO's kernel below
+        alt = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant=v)
+        ref_auto = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="auto")
+        assert oracle.max_err_over_rms(alt.cpu(), ref_auto.cpu()) <= FP32_TOL
     out = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="auto")
-    assert _lib.load().b200fp8_gemm_pick_variant(M, N, K) == _lib.VARIANT_STREAMK
+    assert _lib.load().b200fp8_gemm_pick_variant(M, N, K) == _lib.VARIANT_TILE256
     runtime.check_device_status()
     g = torch.Generator().manual_seed(M)
     blocks = torch.randperm(N // 128, generator=g)[:6].tolist()
@@ -162,7 +170,7 @@ def test_compute_bound_shapes_full_size(device, M, N, K, variant):
     runtime.check_device_status()
 
 
-@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk"])
+@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk"])
 def test_output_view_and_sentinels(device, variant):
     """Output written into a strided view of a sentinel-filled buffer: nothing outside
     [M, N] may change (catches out-of-bounds stores on ragged edges)."""
@@ -194,7 +202,7 @@ def test_strided_inputs(device):
     vA = bigA[:, 128:128 + K].view(torch.float8_e4m3fn)
     vB = bigB[:, :K].view(torch.float8_e4m3fn)
     vAs = bigAs[:, 3:3 + K // 128]
-    for variant in ("tile128", "tile256", "streamk"):
+    for variant in ("tile128", "tile256", "streamk", "tile256_sk"):
         out = runtime.gemm(vA, vB, vAs, Bs.to(device), 128, 128, torch.float32, variant=variant)
         runtime.check_device_status()
         assert oracle.max_err_over_rms(out.cpu(), ref) <= FP32_TOL
