@@ -257,12 +257,16 @@ def main_ours(args):
     slots = torch.empty((world, M, n_local), dtype=torch.bfloat16, device=dev)      # gather buffer, slot r = rank r's columns
     full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
 
+    lin = tp.ShardedFp8Linear(B, Bs) if world > 1 else None
+
     def step(a_bf16):
         """One pass of the hot path on this rank; returns the contiguous [M, N] bf16 result."""
         q, s = pkg.fp8_act_quant(a_bf16)
         if world == 1:
             runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=full)
             return full
+        if args.exchange == "fused":
+            return lin.forward_fused(q, s, torch.bfloat16)
         mine = slots[rank]
         runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=mine)
         dist.all_gather_into_tensor(slots.view(-1), mine.view(-1))
@@ -368,8 +372,11 @@ def main_ours(args):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 accumulate -> bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"N sharded over {world} GPU(s), bf16 all-gather" if world > 1 else "single GPU",
-                       "step": "fp8_act_quant(A bf16) + w8a8_block_fp8_matmul" + (" + all_gather + slot->[M,N] copy" if world > 1 else ""),
+            "config": {"workload": WORKLOAD, "parallelism": f"N sharded over {world} GPU(s), exchange={args.exchange}" if world > 1 else "single GPU",
+                       "step": "fp8_act_quant(A bf16) + w8a8_block_fp8_matmul" + (
+                           "" if world == 1 else
+                           " whose epilogue stores the slice into every GPU's [M,N] buffer over NVLink + 1-element all_reduce as barrier"
+                           if args.exchange == "fused" else " + all_gather + slot->[M,N] copy"),
                        "l2": "per-step traffic (A bf16 117 MB rotating over 2 buffers, C bf16 302 MB) exceeds the 126 MB L2; no flush"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
@@ -400,6 +407,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how the column slices reach every GPU (GEMM epilogue peer stores, or NCCL all-gather)")
     args = ap.parse_args()
     if args.impl == "reference":
         main_reference(args)

@@ -25,6 +25,12 @@ SIGNATURES = {
     "b200fp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                              c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p,
                              c_void_p]),
+    "b200fp8_gemm_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
+                                     c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t,
+                                     c_void_p, c_void_p]),
+    "b200fp8_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "b200fp8_ipc_open": (c_int, [c_void_p, c_void_p]),
+    "b200fp8_ipc_close": (c_int, [c_void_p]),
     "b200fp8_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
     "b200fp8_gemm_pick_variant": (c_int, [c_int64, c_int64, c_int64]),
     "b200fp8_gemm_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstring>
 #include <mutex>
 
 #include "gemm_streamk.cuh"
@@ -54,12 +55,19 @@ int device_info(const DeviceInfo** out) {
         cudaFuncAttributes attr;
         ok = ok && cudaFuncGetAttributes(&attr, fn) == cudaSuccess && attr.numRegs * threads >= regs_needed_total;
       };
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256>), TileCfg<256>::THREADS,
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, false>), TileCfg<256>::THREADS,
+              128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true, false>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_streamk_kernel<256>), StreamKCfg<256>::THREADS,
               128 * StreamKCfg<256>::REGS_CONTROL + 256 * StreamKCfg<256>::REGS_EPILOGUE);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128>), TileCfg<128>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256>), TileCfg<256>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false, false>), TileCfg<128, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, false>), TileCfg<256, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, true, false>), TileCfg<128, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true, false>), TileCfg<256, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, true>), TileCfg<256, false>::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, true>), TileCfg<256>::THREADS,
+              128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<16>), StreamKCfg<16>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<32>), StreamKCfg<32>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<64>), StreamKCfg<64>::SMEM_BYTES);
@@ -228,7 +236,19 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   if (st != B200FP8_OK) return st;
   const int64_t tiles = ((args.M + 127) / 128) * ((args.N + BN - 1) / BN);
   const int grid = sk_grid > 0 ? static_cast<int>(sk_grid) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
-  gemm_tile_kernel<BN><<<grid, TileCfg<BN>::THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, args);
+  if constexpr (BN == 256) {
+    if (args.sk_groups > 0) {
+      gemm_tile_kernel<256, false, true><<<grid, TileCfg<256, false>::THREADS, TileCfg<256, false>::SMEM_BYTES, stream>>>(
+          ta, tb, args);
+      return launch_status();
+    }
+  }
+  if (args.n_dst > 1)
+    gemm_tile_kernel<BN, true, false><<<grid, TileCfg<BN, true>::THREADS, TileCfg<BN, true>::SMEM_BYTES, stream>>>(
+        ta, tb, args);
+  else
+    gemm_tile_kernel<BN, false, false><<<grid, TileCfg<BN, false>::THREADS, TileCfg<BN, false>::SMEM_BYTES, stream>>>(
+        ta, tb, args);
   return launch_status();
 }
 
@@ -336,22 +356,45 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
   return p.ast_bytes + p.partial_bytes;
 }
 
-int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M, int64_t N,
-                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc, int out_dtype,
-                 int variant, void* workspace, size_t workspace_bytes, uint32_t* status_word, void* stream_) {
+// Shared body of b200fp8_gemm (n_dst = 1) and b200fp8_gemm_scatter (n_dst >= 1).
+static int gemm_impl(const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* dst,
+                     const int64_t* dst_ld, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as,
+                     int64_t ld_bs, int out_dtype, int variant, void* workspace, size_t workspace_bytes,
+                     uint32_t* status_word, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (n_dst < 1 || n_dst > 8 || dst == nullptr || dst_ld == nullptr) return B200FP8_ERR_SHAPE;
+  void* C = dst[0];
+  const int64_t ldc = dst_ld[0];
   if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
   if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
   if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_TILE256_SK) return B200FP8_ERR_VARIANT;
   if (M == 0 || N == 0) return B200FP8_OK;
-  if (C == nullptr) return B200FP8_ERR_NULL;
-  if (ldc < N) return B200FP8_ERR_SHAPE;
+  for (int d = 0; d < n_dst; ++d) {
+    if (dst[d] == nullptr) return B200FP8_ERR_NULL;
+    if (dst_ld[d] < N) return B200FP8_ERR_SHAPE;
+  }
 
   const DeviceInfo* dev = nullptr;
   int st = device_info(&dev);
   if (st != B200FP8_OK) return st;
 
+  // 16-byte vector stores through the staging path need aligned destinations
+  const int64_t esize = out_dtype == B200FP8_OUT_FP32 ? 4 : 2;
+  bool staged = (N * esize) % 16 == 0;
+  for (int d = 0; d < n_dst; ++d)
+    staged = staged && (reinterpret_cast<uintptr_t>(dst[d]) & 15u) == 0 && (dst_ld[d] * esize) % 16 == 0;
+  if (n_dst > 1 && !staged) return B200FP8_ERR_ALIGN;
+  auto fill_dst = [&](GemmArgs& a) {
+    a.n_dst = n_dst;
+    a.staged_store = staged ? 1 : 0;
+    for (int d = 0; d < 8; ++d) {
+      a.dst[d] = d < n_dst ? dst[d] : nullptr;
+      a.dst_ld[d] = d < n_dst ? dst_ld[d] : 0;
+    }
+  };
+
   if (K == 0) {
+    if (n_dst > 1) return B200FP8_ERR_SHAPE;
     gemm_zero_fill_kernel<<<dev->sm_count, 256, 0, stream>>>(C, M, N, ldc, out_dtype == B200FP8_OUT_FP32);
     return launch_status();
   }
@@ -364,6 +407,7 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
+  if (n_dst > 1 && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
 
   if (variant == B200FP8_VARIANT_TILE256_SK) {
     if (M > 256) return B200FP8_ERR_VARIANT;
@@ -373,6 +417,7 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
       return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
+    fill_dst(args);
     args.sk_groups = p.groups;
     args.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + p.ast_bytes);
     args.AsT = static_cast<const float*>(workspace);
@@ -411,6 +456,7 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
+    fill_dst(args);
     args.sk_groups = 0;
     args.partial = nullptr;
     args.AsT = static_cast<const float*>(workspace);
@@ -479,6 +525,71 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   streamk_fixup_kernel<<<fix_grid, 128, 0, stream>>>(
       partial, C, M, N, p.num_kb, ldc, out_dtype == B200FP8_OUT_FP32, p.mp, p.grid);
   return launch_status();
+}
+
+int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M, int64_t N,
+                 int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc, int out_dtype,
+                 int variant, void* workspace, size_t workspace_bytes, uint32_t* status_word, void* stream) {
+  void* dst[1] = {C};
+  const int64_t ld[1] = {ldc};
+  return gemm_impl(A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
+                   workspace_bytes, status_word, stream);
+}
+
+int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* C_dst,
+                         const int64_t* ldc_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int64_t ld_as, int64_t ld_bs, int out_dtype, int variant, void* workspace,
+                         size_t workspace_bytes, uint32_t* status_word, void* stream) {
+  return gemm_impl(A, B, As, Bs, n_dst, C_dst, ldc_dst, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant,
+                   workspace, workspace_bytes, status_word, stream);
+}
+
+int b200fp8_ipc_export(const void* ptr, void* handle_out_64, int64_t* offset_out) {
+  if (ptr == nullptr || handle_out_64 == nullptr || offset_out == nullptr) return B200FP8_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  // the handle names the whole allocation; the offset of ptr inside it comes from the driver
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+    cudaGetLastError();
+    return B200FP8_ERR_DRIVER;
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (reinterpret_cast<RangeFn>(sym)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS)
+    return B200FP8_ERR_DRIVER;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP8_ERR_DRIVER;
+  }
+  memcpy(handle_out_64, &h, 64);
+  *offset_out = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return B200FP8_OK;
+}
+
+int b200fp8_ipc_open(const void* handle_64, void** base_out) {
+  if (handle_64 == nullptr || base_out == nullptr) return B200FP8_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || p == nullptr) {
+    cudaGetLastError();
+    return B200FP8_ERR_DRIVER;
+  }
+  *base_out = p;
+  return B200FP8_OK;
+}
+
+int b200fp8_ipc_close(void* base) {
+  if (base == nullptr) return B200FP8_ERR_NULL;
+  if (cudaIpcCloseMemHandle(base) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP8_ERR_DRIVER;
+  }
+  return B200FP8_OK;
 }
 
 int b200fp8_gemm_decode_static(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M,

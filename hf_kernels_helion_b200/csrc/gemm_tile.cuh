@@ -53,6 +53,15 @@ struct GemmArgs {
   // slot = 2 * cta + (0 for the CTA's first segment, 1 for a later one).
   int sk_groups;
   float* partial;
+  // Destinations of the result: dst[0] is C itself; dst[1..n_dst-1] are further buffers that
+  // receive the same [M, N] block (other GPUs' output buffers mapped into this process, for
+  // the N-sharded multi-GPU case). staged_store = 1 when every destination allows 16-byte
+  // vector stores (pointer and row pitch multiples of 16 bytes, N * element size too): the
+  // tile then goes through shared memory and is written as whole 128-byte row pieces.
+  int n_dst;
+  int staged_store;
+  void* dst[8];
+  int64_t dst_ld[8];
   const float* AsT;   // [ceil(K/128)][m_pad] token scales, K-block-major (written by tile_prep_kernel)
   int64_t m_pad;      // M rounded up to 128
   const float* As;
@@ -67,7 +76,7 @@ struct GemmArgs {
 #endif
 };
 
-template <int BN_>
+template <int BN_, bool MULTI_ = false>
 struct TileCfg {
   static constexpr int BM = 128;
   static constexpr int BN = BN_;
@@ -96,7 +105,13 @@ struct TileCfg {
   static constexpr int TMEM_STAGES = 512 / BN_;     // accumulator stages in TMEM (all 512 columns are used)
   static constexpr int TMEM_COLS = TMEM_STAGES * BN_;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
+  // output staging: each epilogue warp owns 32 rows x 128 bytes (128-byte-swizzled)
+  static constexpr int OUT_STAGE_BYTES_PER_WARP = 32 * 128;
+  // (only the multi-destination kernel stages its output; the single-destination kernel
+  // stores straight from registers and keeps the shared memory and registers for the main loop)
+  static constexpr bool MULTI = MULTI_;
+  static constexpr int OUT_STAGE_BYTES = MULTI_ ? EPI_WARPS * OUT_STAGE_BYTES_PER_WARP : 0;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + BAR_BYTES + 1024;  // +1024: alignment slack
 };
 
 // Tile order: panels of kRasterGroup M-blocks; inside a panel the M index runs fastest, then
@@ -126,12 +141,13 @@ struct SegCursor {
   bool started;
 };
 
+template <bool SK>
 __device__ __forceinline__ SegCursor seg_begin(int sk_groups, int num_m, int num_n, int num_kb) {
   SegCursor c;
   c.tile = static_cast<int>(blockIdx.x);
   c.started = false;
   c.u = c.u1 = 0;
-  if (sk_groups > 0) {
+  if constexpr (SK) {
     const int64_t total = static_cast<int64_t>(num_n) * num_kb;
     const int64_t g = blockIdx.x / num_m;
     c.u = streamk_first_unit(g, total, sk_groups);
@@ -141,18 +157,22 @@ __device__ __forceinline__ SegCursor seg_begin(int sk_groups, int num_m, int num
 }
 
 // Number of K blocks this CTA processes in total.
+template <bool SK>
 __device__ __forceinline__ uint32_t seg_total_kblocks(const SegCursor& c, int sk_groups, int num_tiles, int num_kb) {
-  if (sk_groups > 0) return static_cast<uint32_t>(c.u1 - c.u);
+  (void)sk_groups;
+  if constexpr (SK) return static_cast<uint32_t>(c.u1 - c.u);
   const int mine = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                    static_cast<int>(gridDim.x);
   return static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
 }
 
+template <bool SK>
 __device__ __forceinline__ bool seg_next(SegCursor& c, int sk_groups, int num_m, int num_n, int num_kb, int num_tiles,
                                          Segment& s) {
+  (void)sk_groups;
   s.first = !c.started;
   c.started = true;
-  if (sk_groups > 0) {
+  if constexpr (SK) {
     if (c.u >= c.u1) return false;
     s.m_blk = static_cast<int>(blockIdx.x % num_m);
     s.n_blk = static_cast<int>(c.u / num_kb);
@@ -161,26 +181,28 @@ __device__ __forceinline__ bool seg_next(SegCursor& c, int sk_groups, int num_m,
     s.kb_end = (num_kb - s.kb_begin) < left ? num_kb : s.kb_begin + static_cast<int>(left);
     c.u += s.kb_end - s.kb_begin;
     return true;
-  }
+  } else {
   if (c.tile >= num_tiles) return false;
   tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
   s.kb_begin = 0;
   s.kb_end = num_kb;
   c.tile += static_cast<int>(gridDim.x);
   return true;
+  }
 }
 
-template <int BN>
-__global__ void __launch_bounds__(TileCfg<BN>::THREADS, 1)
+template <int BN, bool MULTI, bool SK>
+__global__ void __launch_bounds__(TileCfg<BN, MULTI>::THREADS, 1)
 gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs args) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, MULTI>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* out_stage = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::OUT_STAGE_BYTES);
   uint64_t* full = bars;                  // [STAGES]  TMA bytes landed
   uint64_t* empty = bars + STAGES;        // [STAGES]  MMA finished reading the slot
   uint64_t* tfull = bars + 2 * STAGES;    // [TS]      TMEM stage holds a finished K-block partial
@@ -230,9 +252,9 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       prefetch_tmap(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
-      SegCursor cur = seg_begin(args.sk_groups, num_m, num_n, num_kb);
+      SegCursor cur = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
       Segment seg;
-      while (ok && seg_next(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+      while (ok && seg_next<SK>(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
         const int m0 = seg.m_blk * Cfg::BM;
         const int n0 = seg.n_blk * BN;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
@@ -274,8 +296,8 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t it = 0;
     uint32_t last = 0xffffffffu;
     bool ok = true;
-    const SegCursor cur0 = seg_begin(args.sk_groups, num_m, num_n, num_kb);
-    const uint32_t total_it = seg_total_kblocks(cur0, args.sk_groups, num_tiles, num_kb);
+    const SegCursor cur0 = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
+    const uint32_t total_it = seg_total_kblocks<SK>(cur0, args.sk_groups, num_tiles, num_kb);
     {
       for (; it < total_it; ++it) {
         if ((it & 1u) != p) continue;
@@ -328,9 +350,9 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
     bool ok = true;
-    SegCursor cur = seg_begin(args.sk_groups, num_m, num_n, num_kb);
+    SegCursor cur = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
     Segment seg;
-    while (ok && seg_next(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+    while (ok && seg_next<SK>(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
       const int m0 = seg.m_blk * Cfg::BM;
       const int n0 = seg.n_blk * BN;
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
@@ -424,7 +446,7 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!ok) break;
 
 #define ACC(i) (((i) & 1) ? acc[(i) >> 5][((i) & 31) >> 1].y : acc[(i) >> 5][((i) & 31) >> 1].x)
-      if (seg.kb_begin != 0 || seg.kb_end != num_kb) {
+      if (SK && (seg.kb_begin != 0 || seg.kb_end != num_kb)) {
         // stream-K: this CTA saw only part of the K range - leave the fp32 partial sums of the
         // rows that exist in the workspace; tile_sk_fixup_kernel adds the pieces of the tile
         if (row < M) {
@@ -433,6 +455,67 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int j = 0; j < Cfg::EPI_COLS; j += 4)
             *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
+        }
+      } else if (MULTI && args.staged_store) {
+        // Full tile, vector-store path: 128 bytes of each of this warp's 32 rows per pass go
+        // to the warp's staging area (16-byte chunks XOR-swizzled by row so that neither the
+        // row-wise writes nor the 4-rows-per-instruction reads conflict), then every lane
+        // writes 16 bytes so that a warp store covers four complete 128-byte row pieces - for
+        // every destination buffer.
+        uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
+        const int esize = args.out_fp32 ? 4 : 2;
+        const int cols_per_pass = 128 / esize;
+        const int passes = Cfg::EPI_COLS / cols_per_pass;
+        const int64_t n_bytes = N * esize;
+        for (int p = 0; p < passes; ++p) {
+          __syncwarp();
+          if (args.out_fp32) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float4 v4;
+              const int j0 = c * 4;
+              // columns of this pass start at p * 32: select with a runtime p over unrolled j
+              v4.x = 0.f; v4.y = 0.f; v4.z = 0.f; v4.w = 0.f;
+#pragma unroll
+              for (int pp = 0; pp < Cfg::EPI_COLS / 32; ++pp)
+                if (pp == p) v4 = make_float4(ACC(pp * 32 + j0), ACC(pp * 32 + j0 + 1), ACC(pp * 32 + j0 + 2), ACC(pp * 32 + j0 + 3));
+              *reinterpret_cast<float4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = v4;
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint4 u = make_uint4(0u, 0u, 0u, 0u);
+              const int j0 = c * 8;
+#pragma unroll
+              for (int pp = 0; pp < Cfg::EPI_COLS / 64; ++pp)
+                if (pp == p) {
+                  __nv_bfloat162 v0 = __floats2bfloat162_rn(ACC(pp * 64 + j0), ACC(pp * 64 + j0 + 1));
+                  __nv_bfloat162 v1 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 2), ACC(pp * 64 + j0 + 3));
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 4), ACC(pp * 64 + j0 + 5));
+                  __nv_bfloat162 v3 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 6), ACC(pp * 64 + j0 + 7));
+                  u.x = *reinterpret_cast<uint32_t*>(&v0);
+                  u.y = *reinterpret_cast<uint32_t*>(&v1);
+                  u.z = *reinterpret_cast<uint32_t*>(&v2);
+                  u.w = *reinterpret_cast<uint32_t*>(&v3);
+                }
+              *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = u;
+            }
+          }
+          __syncwarp();
+          const int cc = lane & 7;
+          const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + cc * 16;
+          if (col_byte + 16 <= n_bytes) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = (lane >> 3) + 4 * i;
+              const int64_t grow = static_cast<int64_t>(m0) + q * 32 + rr;
+              if (grow < M) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_w + rr * 128 + ((cc ^ (rr & 7)) << 4));
+                for (int d = 0; d < args.n_dst; ++d)
+                  *reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.dst[d]) + grow * args.dst_ld[d] * esize + col_byte) = v;
+              }
+            }
+          }
         }
       } else
       if (row < M && col0 < N) {

@@ -135,6 +135,44 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
     return out
 
 
+def gemm_scatter(A, B, As, Bs, dst_ptrs, dst_lds, out_dtype: torch.dtype, variant=None) -> None:
+    """C = A @ B.T written into several [M, >= N] buffers at once (b200fp8_gemm_scatter).
+    dst_ptrs[0] / dst_lds[0] describe this GPU's own buffer, the others are device addresses of
+    peer buffers mapped into this process (see PeerBuffers in tp.py); all point at the first
+    element of this call's column slice.  Shapes and dtypes as for gemm(); inputs must already
+    be row-major views the kernels can address."""
+    import ctypes
+
+    if out_dtype not in _OUT_CODES:
+        raise ValueError(f"output dtype must be torch.bfloat16 or torch.float32, got {out_dtype}")
+    _require_cuda(A, "A")
+    M, K = A.shape
+    N = B.shape[0]
+    n = len(dst_ptrs)
+    if n < 1 or n > 8 or len(dst_lds) != n:
+        raise ValueError("between 1 and 8 destinations, one leading dimension each")
+    if M == 0 or N == 0:
+        return
+    dev = A.device
+    lib = _lib.load()
+    A_, B_ = _row_major(A, 16), _row_major(B, 16)
+    As_, Bs_ = _row_major(As, 1), _row_major(Bs, 1)
+    v = resolve_variant(variant)
+    ptrs = (ctypes.c_void_p * n)(*[int(p) for p in dst_ptrs])
+    lds = (ctypes.c_int64 * n)(*[int(x) for x in dst_lds])
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200fp8_gemm_workspace_bytes(M, N, K, v))
+        if ws_bytes < 0:
+            _lib.check(-ws_bytes, "b200fp8_gemm_workspace_bytes")
+        ws = _workspace(dev, ws_bytes) if ws_bytes > 0 else None
+        st = lib.b200fp8_gemm_scatter(
+            A_.data_ptr(), B_.data_ptr(), As_.data_ptr(), Bs_.data_ptr(), n, ptrs, lds,
+            M, N, K, _ld(A_), _ld(B_), _ld(As_), _ld(Bs_), _OUT_CODES[out_dtype], v,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "b200fp8_gemm_scatter")
+
+
 def _quant_common(x: torch.Tensor, name: str):
     if x.dim() != 2:
         raise ValueError(f"{name} must be 2-D, got shape {tuple(x.shape)}")

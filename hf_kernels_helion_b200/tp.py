@@ -32,6 +32,53 @@ def shard_weight(B: torch.Tensor, Bs: torch.Tensor, world: int, rank: int, block
     return B[n0:n1], Bs[n0 // block_n:n1 // block_n]
 
 
+class PeerBuffers:
+    """One [M, N] output buffer per rank, each mapped into every process of the group
+    (CUDA IPC), so that a kernel on any GPU can store into all of them over NVLink.
+    ptr(r) is the device address, valid in THIS process, of rank r's buffer."""
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device: torch.device, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.local = torch.empty((M, N), dtype=dtype, device=device)
+        lib = _lib.load()
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_int64(0)
+        with torch.cuda.device(device):
+            _lib.check(lib.b200fp8_ipc_export(self.local.data_ptr(), handle, ctypes.byref(offset)), "b200fp8_ipc_export")
+            metas = [None] * self.world
+            dist.all_gather_object(metas, (bytes(handle.raw), int(offset.value)), group=group)
+            self._bases = {}
+            self._ptrs = [0] * self.world
+            for r, (h, off) in enumerate(metas):
+                if r == self.rank:
+                    self._ptrs[r] = self.local.data_ptr()
+                    continue
+                base = ctypes.c_void_p(0)
+                _lib.check(lib.b200fp8_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(base)), "b200fp8_ipc_open")
+                self._bases[r] = base
+                self._ptrs[r] = int(base.value) + off
+        dist.barrier(group)
+
+    def ptr(self, r: int) -> int:
+        return self._ptrs[r]
+
+    def close(self) -> None:
+        from . import _lib
+
+        torch.cuda.synchronize()
+        dist.barrier(self.group)          # nobody may still be storing into a buffer that is about to be unmapped
+        lib = _lib.load()
+        for base in self._bases.values():
+            lib.b200fp8_ipc_close(base)
+        self._bases = {}
+
+
 class ShardedFp8Linear:
     """Holds this rank's weight slice and runs  C = A . B^T  tensor-parallel.
 
@@ -94,6 +141,38 @@ class ShardedFp8Linear:
         if self.world > 1:
             dist.all_gather_into_tensor(buf.view(-1), mine.reshape(-1), group=self.group)
         return buf
+
+    def forward_fused(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
+        """Contiguous C [M, N] on every rank with the exchange fused into the GEMM: the kernel's
+        epilogue stores this rank's column slice into the [M, N] buffer of EVERY rank (peer
+        stores over NVLink), and one tiny all-reduce afterwards is the barrier that tells each
+        rank that all slices have arrived.  No all-gather, no transpose copy.
+
+        Two buffer sets alternate between calls: the result returned by call i stays valid until
+        call i + 2 is issued, and work that reads it must be enqueued on the current stream
+        before call i + 1 (whose barrier then orders it before any peer's later overwrite)."""
+        from . import runtime  # noqa: PLC0415
+
+        M = A.shape[0]
+        key = (M, output_dtype, A.device)
+        if getattr(self, "_peer_key", None) != key:
+            for pb in getattr(self, "_peer", []):
+                pb.close()
+            self._peer = [PeerBuffers(M, self.N, output_dtype, A.device, self.group) for _ in range(2)]
+            self._peer_key = key
+            self._peer_turn = 0
+            self._flag = torch.zeros(1, dtype=torch.float32, device=A.device)
+        pb = self._peer[self._peer_turn]
+        self._peer_turn ^= 1
+        esize = pb.local.element_size()
+        col_bytes = self.rank * self.n_local * esize
+        # start the remote stores at different peers on different ranks
+        order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
+        ptrs = [pb.ptr(r) + col_bytes for r in order]
+        runtime.gemm_scatter(A, self.B, As, self.Bs, ptrs, [self.N] * self.world, output_dtype)
+        if self.world > 1:
+            dist.all_reduce(self._flag, group=self.group)
+        return pb.local
 
     def forward(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
         """Contiguous C [M, N] on every rank (all-gather, then one transpose copy of the slots)."""

@@ -129,6 +129,40 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
                  void* workspace, size_t workspace_bytes,
                  uint32_t* status_word, void* stream);
 
+/*
+ * b200fp8_gemm writing the same [M, N] result into n_dst (1..8) buffers, C_dst[0] being the
+ * caller's own. No counterpart in the reference (which has no multi-GPU code); it is the
+ * compute + exchange step of the N-sharded layout derived from
+ * torch-ext/finegrained_fp8_helion/fp8.py:30-36: every GPU computes its column slice and
+ * stores it straight into the full-width output buffer of every GPU of the node, so that no
+ * separate all-gather pass is needed. C_dst[d] points at the first element of THIS call's
+ * column slice inside destination d (a peer buffer opened with b200fp8_ipc_open, plus the
+ * slice's column offset), ldc_dst[d] is that buffer's row pitch in elements.
+ * Remote destinations are written with plain 16-byte stores over NVLink from a staged tile
+ * (no TMA, no multicast). Every C_dst[d] must be 16-byte aligned, ldc_dst[d] and N multiples
+ * of 16 bytes worth of elements; only the tile variants (or AUTO resolving to one) are
+ * allowed. The stores are complete when the kernel is; the caller synchronises the GPUs
+ * (stream order + a barrier between ranks) before any of them reads its buffer.
+ */
+int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const float* Bs,
+                         int n_dst, void* const* C_dst, const int64_t* ldc_dst,
+                         int64_t M, int64_t N, int64_t K,
+                         int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs,
+                         int out_dtype, int variant,
+                         void* workspace, size_t workspace_bytes,
+                         uint32_t* status_word, void* stream);
+
+/*
+ * CUDA IPC helpers for b200fp8_gemm_scatter (no counterpart in the reference). export: a
+ * 64-byte handle of the device allocation that contains ptr, and ptr's byte offset inside it;
+ * the handle travels to the other process by any host channel. open: maps that allocation
+ * into the calling process with the CURRENT device as the accessing GPU (peer access is
+ * enabled on demand) and returns its base; close unmaps it.
+ */
+int b200fp8_ipc_export(const void* ptr, void* handle_out_64, int64_t* offset_out);
+int b200fp8_ipc_open(const void* handle_64, void** base_out);
+int b200fp8_ipc_close(void* base);
+
 /* Bytes of workspace b200fp8_gemm needs for this call (0 when none). Negative = error status, negated. */
 int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
 

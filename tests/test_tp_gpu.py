@@ -33,6 +33,12 @@ def _worker(rank, world, port, q):
         runtime.check_device_status()
         ref = oracle.gemm_dequant(A, B, As, Bs)
         ok = out.shape == (M, N) and oracle.bf16_ulp_error(out.cpu(), ref) <= 1
+        # exchange fused into the GEMM epilogue (peer stores): same values, three calls to cycle the buffers
+        for _ in range(3):
+            fused = lin.forward_fused(A.to(dev), As.to(dev), torch.bfloat16)
+            torch.cuda.synchronize()
+            ok = ok and fused.shape == (M, N) and torch.equal(fused, out)
+        runtime.check_device_status()
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
