@@ -236,19 +236,32 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   if (st != B200FP8_OK) return st;
   const int64_t tiles = ((args.M + 127) / 128) * ((args.N + BN - 1) / BN);
   const int grid = sk_grid > 0 ? static_cast<int>(sk_grid) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
-  if constexpr (BN == 256) {
-    if (args.sk_groups > 0) {
-      gemm_tile_kernel<256, false, true><<<grid, TileCfg<256, false>::THREADS, TileCfg<256, false>::SMEM_BYTES, stream>>>(
-          ta, tb, args);
-      return launch_status();
-    }
+  // Programmatic dependent launch: the kernel may begin (barrier set-up, TMEM allocation,
+  // operand loads) while the tile_prep_kernel enqueued just before it is still running.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(TileCfg<BN, false>::THREADS);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t err;
+  if (BN == 256 && args.sk_groups > 0) {
+    cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, false, true>, ta, tb, args);
+  } else if (args.n_dst > 1) {
+    cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, true, false>, ta, tb, args);
+  } else {
+    cfg.dynamicSmemBytes = TileCfg<BN, false>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, false, false>, ta, tb, args);
   }
-  if (args.n_dst > 1)
-    gemm_tile_kernel<BN, true, false><<<grid, TileCfg<BN, true>::THREADS, TileCfg<BN, true>::SMEM_BYTES, stream>>>(
-        ta, tb, args);
-  else
-    gemm_tile_kernel<BN, false, false><<<grid, TileCfg<BN, false>::THREADS, TileCfg<BN, false>::SMEM_BYTES, stream>>>(
-        ta, tb, args);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP8_ERR_LAUNCH;
+  }
   return launch_status();
 }
 

@@ -350,6 +350,9 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
     bool ok = true;
+    // the scale copy AsT is written by the preceding tile_prep_kernel; with programmatic
+    // dependent launch this kernel may have started before that grid finished
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     SegCursor cur = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
     Segment seg;
     while (ok && seg_next<SK>(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
@@ -612,6 +615,10 @@ tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int6
 __global__ void __launch_bounds__(256)
 tile_prep_kernel(const float* __restrict__ As, float* __restrict__ AsT, int64_t M, int64_t m_pad, int num_kb,
                  int64_t ld_as) {
+  // let the GEMM kernel that follows (launched with programmatic stream serialisation) start
+  // its prologue and operand loads now; its epilogue warps wait for this grid before they
+  // read AsT
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float t[32][33];
   const int64_t m0 = static_cast<int64_t>(blockIdx.x) * 32;
   const int kb0 = blockIdx.y * 32;
