@@ -179,9 +179,11 @@ StreamKPlan streamk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
 }
 
 // tile variants: AsT [ceil(K/128)][M rounded up to 128] fp32
+int64_t tile_ast_bytes(int64_t M, int64_t K) { return align_up(((K + 127) / 128) * align_up(M, 128) * 4, 256); }
+// + a 16-row zero-padded copy of A when M < 16
 int64_t tile_workspace_bytes(int64_t M, int64_t K) {
   if (M == 0 || K == 0) return 0;
-  return align_up(((K + 127) / 128) * align_up(M, 128) * 4, 256);
+  return tile_ast_bytes(M, K) + (M < 16 ? 16 * align_up(K, 16) : 0);
 }
 
 // tile stream-K (128x256 tiles, M <= 256): groups of num_m CTAs share the (N tile, K block) units
@@ -230,7 +232,7 @@ template <int BN>
 int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb, int sm_count,
                 cudaStream_t stream, int64_t sk_grid = 0) {
   CUtensorMap ta, tb;
-  int st = make_tmap_u8(&ta, A, args.M, args.K, lda, 128);
+  int st = make_tmap_u8(&ta, A, args.a_from_prep ? 16 : args.M, args.K, lda, 128);
   if (st != B200FP8_OK) return st;
   st = make_tmap_u8(&tb, B, args.N, args.K, ldb, BN);
   if (st != B200FP8_OK) return st;
@@ -431,14 +433,17 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
     fill_dst(args);
+    uint8_t* a_pad = M < 16 ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
+    args.a_from_prep = a_pad != nullptr;
     args.sk_groups = p.groups;
     args.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + p.ast_bytes);
     args.AsT = static_cast<const float*>(workspace);
     args.m_pad = align_up(M, 128);
     {
       const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
-      tile_prep_kernel<<<grid, 256, 0, stream>>>(As, static_cast<float*>(workspace), M, args.m_pad,
-                                                 static_cast<int>(kblocks), ld_as);
+      tile_prep_kernel<<<dim3(grid.x, grid.y, a_pad != nullptr ? 2u : 1u), 256, 0, stream>>>(
+          As, static_cast<float*>(workspace), M, args.m_pad, static_cast<int>(kblocks), ld_as,
+          static_cast<const uint8_t*>(A), a_pad, K, lda, align_up(K, 16));
       st = launch_status();
       if (st != B200FP8_OK) return st;
     }
@@ -456,7 +461,7 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
 #ifdef B200FP8_TRACE
     args.trace = nullptr;
 #endif
-    st = launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream, p.grid);
+    st = launch_tile<256>(a_pad ? a_pad : A, B, args, a_pad ? align_up(K, 16) : lda, ldb, dev->sm_count, stream, p.grid);
     if (st != B200FP8_OK) return st;
     const dim3 fix_grid(static_cast<unsigned>(p.num_n * p.num_m), 16u);
     tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, p.num_kb, ldc,
@@ -470,14 +475,17 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
     fill_dst(args);
+    uint8_t* a_pad = M < 16 ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
+    args.a_from_prep = a_pad != nullptr;
     args.sk_groups = 0;
     args.partial = nullptr;
     args.AsT = static_cast<const float*>(workspace);
     args.m_pad = align_up(M, 128);
     {
       const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
-      tile_prep_kernel<<<grid, 256, 0, stream>>>(As, static_cast<float*>(workspace), M, args.m_pad,
-                                                 static_cast<int>(kblocks), ld_as);
+      tile_prep_kernel<<<dim3(grid.x, grid.y, a_pad != nullptr ? 2u : 1u), 256, 0, stream>>>(
+          As, static_cast<float*>(workspace), M, args.m_pad, static_cast<int>(kblocks), ld_as,
+          static_cast<const uint8_t*>(A), a_pad, K, lda, align_up(K, 16));
       st = launch_status();
       if (st != B200FP8_OK) return st;
     }
@@ -495,8 +503,10 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
 #ifdef B200FP8_TRACE
     args.trace = reinterpret_cast<long long*>(status_word) + 1;  // trace builds: event buffer follows the status word
 #endif
-    return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(A, B, args, lda, ldb, dev->sm_count, stream)
-                                              : launch_tile<256>(A, B, args, lda, ldb, dev->sm_count, stream);
+    const void* a_eff = a_pad ? static_cast<const void*>(a_pad) : A;
+    const int64_t lda_eff = a_pad ? align_up(K, 16) : lda;
+    return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream)
+                                              : launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream);
   }
 
   // stream-K decode variant
