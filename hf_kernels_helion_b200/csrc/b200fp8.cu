@@ -55,18 +55,18 @@ int device_info(const DeviceInfo** out) {
         cudaFuncAttributes attr;
         ok = ok && cudaFuncGetAttributes(&attr, fn) == cudaSuccess && attr.numRegs * threads >= regs_needed_total;
       };
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, false>), TileCfg<256>::THREADS,
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true, false>), TileCfg<256>::THREADS,
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_streamk_kernel<256>), StreamKCfg<256>::THREADS,
               128 * StreamKCfg<256>::REGS_CONTROL + 256 * StreamKCfg<256>::REGS_EPILOGUE);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false, false>), TileCfg<128, false>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, false>), TileCfg<256, false>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, true, false>), TileCfg<128, true>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true, false>), TileCfg<256, true>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, true>), TileCfg<256, false>::SMEM_BYTES);
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false, true>), TileCfg<256>::THREADS,
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false>), TileCfg<128, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256, false>::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<16>), StreamKCfg<16>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<32>), StreamKCfg<32>::SMEM_BYTES);
@@ -252,13 +252,21 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   cudaError_t err;
   if (BN == 256 && args.sk_groups > 0) {
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, false, true>, ta, tb, args);
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, true>, ta, tb, args);
   } else if (args.n_dst > 1) {
+    // one byte-matrix tensor map per destination: [M rows, N * element size], 32 x 128-byte boxes
+    DstMaps dm;
+    const int64_t esize = args.out_fp32 ? 4 : 2;
+    for (int d = 0; d < 8; ++d) {
+      const int src = d < args.n_dst ? d : 0;
+      st = make_tmap_u8(&dm.m[d], args.dst[src], args.M, args.N * esize, args.dst_ld[src] * esize, 32);
+      if (st != B200FP8_OK) return st;
+    }
     cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, true, false>, ta, tb, args);
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_multi_kernel<BN>, ta, tb, args, dm);
   } else {
     cfg.dynamicSmemBytes = TileCfg<BN, false>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, false, false>, ta, tb, args);
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, false>, ta, tb, args);
   }
   if (err != cudaSuccess) {
     cudaGetLastError();

@@ -55,9 +55,9 @@ struct GemmArgs {
   float* partial;
   // Destinations of the result: dst[0] is C itself; dst[1..n_dst-1] are further buffers that
   // receive the same [M, N] block (other GPUs' output buffers mapped into this process, for
-  // the N-sharded multi-GPU case). staged_store = 1 when every destination allows 16-byte
-  // vector stores (pointer and row pitch multiples of 16 bytes, N * element size too): the
-  // tile then goes through shared memory and is written as whole 128-byte row pieces.
+  // the N-sharded multi-GPU case). staged_store = 1 when every destination meets the TMA
+  // rules (pointer and row pitch multiples of 16 bytes): the multi-destination kernel then
+  // stages the tile in shared memory and sends it with asynchronous TMA stores.
   int a_from_prep;   // 1: A was re-laid by tile_prep_kernel (M < 16 padded to 16 rows), the producer must wait for it
   int n_dst;
   int staged_store;
@@ -192,10 +192,15 @@ __device__ __forceinline__ bool seg_next(SegCursor& c, int sk_groups, int num_m,
   }
 }
 
+// Tensor maps of the destinations of the multi-destination kernel: byte matrices
+// [M rows, N * element size] with box 32 rows x 128 bytes, SWIZZLE_128B.
+struct DstMaps {
+  CUtensorMap m[8];
+};
+
 template <int BN, bool MULTI, bool SK>
-__global__ void __launch_bounds__(TileCfg<BN, MULTI>::THREADS, 1)
-gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmArgs args) {
+__device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                               const GemmArgs& args, const CUtensorMap* dmaps) {
   using Cfg = TileCfg<BN, MULTI>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
@@ -462,17 +467,16 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
         }
       } else if (MULTI && args.staged_store) {
-        // Full tile, vector-store path: 128 bytes of each of this warp's 32 rows per pass go
-        // to the warp's staging area (16-byte chunks XOR-swizzled by row so that neither the
-        // row-wise writes nor the 4-rows-per-instruction reads conflict), then every lane
-        // writes 16 bytes so that a warp store covers four complete 128-byte row pieces - for
-        // every destination buffer.
+        // Full tile, multi-destination path: per pass, 128 bytes of each of this warp's 32 rows
+        // go to the warp's staging area in the SWIZZLE_128B pattern (16-byte chunk index XOR
+        // row % 8, conflict-free for the row-wise writes), and one TMA store per destination
+        // ships the 32 x 128-byte box; rows and columns beyond [M, N] are clipped by the TMA.
         uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
         const int esize = args.out_fp32 ? 4 : 2;
         const int cols_per_pass = 128 / esize;
         const int passes = Cfg::EPI_COLS / cols_per_pass;
-        const int64_t n_bytes = N * esize;
         for (int p = 0; p < passes; ++p) {
+          if (lane == 0) bulk_wait_group_read0();   // the previous box has left the staging buffer
           __syncwarp();
           if (args.out_fp32) {
 #pragma unroll
@@ -506,20 +510,15 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = u;
             }
           }
+          // generic-proxy writes above -> visible to the async proxy, then one lane sends the
+          // box to every destination; the copies run on while the warp goes back to the K loop
+          fence_proxy_async_smem();
           __syncwarp();
-          const int cc = lane & 7;
-          const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + cc * 16;
-          if (col_byte + 16 <= n_bytes) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = (lane >> 3) + 4 * i;
-              const int64_t grow = static_cast<int64_t>(m0) + q * 32 + rr;
-              if (grow < M) {
-                const uint4 v = *reinterpret_cast<const uint4*>(stage_w + rr * 128 + ((cc ^ (rr & 7)) << 4));
-                for (int d = 0; d < args.n_dst; ++d)
-                  *reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.dst[d]) + grow * args.dst_ld[d] * esize + col_byte) = v;
-              }
-            }
+          if (lane == 0) {
+            const int32_t col_byte = col0 * esize + p * 128;
+            const int32_t row0 = m0 + q * 32;
+            for (int d = 0; d < args.n_dst; ++d) tma_store_2d(&dmaps[d], stage_w, col_byte, row0);
+            bulk_commit_group();
           }
         }
       } else
@@ -563,6 +562,10 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #undef ACC
 
   // ------------------------------------------------------------------ teardown
+  if constexpr (MULTI) {
+    // the output copies of this warp must be complete (written) before the CTA exits
+    if (warp >= 4 && lane == 0) bulk_wait_group0();
+  }
   __syncwarp();
   tc_fence_before();
   __syncthreads();
@@ -570,6 +573,22 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+}
+
+template <int BN, bool SK>
+__global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
+gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs args) {
+  gemm_tile_body<BN, false, SK>(tmap_a, tmap_b, args, nullptr);
+}
+
+// Multi-destination form: the finished tile is staged in shared memory and sent to every
+// destination (this GPU's and its peers' output buffers) by asynchronous TMA stores.
+template <int BN>
+__global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
+gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
+  gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
 }
 
 // Stream-K mode: adds the fp32 pieces of every output tile whose K range was split between
