@@ -255,7 +255,9 @@ def main_ours(args):
     del w
     n_local = n1 - n0
     slots = torch.empty((world, M, n_local), dtype=torch.bfloat16, device=dev)      # gather buffer, slot r = rank r's columns
-    full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    fulls = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]   # results alternate between two buffers
+    full = fulls[0]
+    turn = [0]
 
     lin = tp.ShardedFp8Linear(B, Bs) if world > 1 else None
 
@@ -263,15 +265,19 @@ def main_ours(args):
         """One pass of the hot path on this rank; returns the contiguous [M, N] bf16 result."""
         q, s = pkg.fp8_act_quant(a_bf16)
         if world == 1:
-            runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=full)
-            return full
+            out = fulls[turn[0]]
+            turn[0] ^= 1
+            runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=out)
+            return out
         if args.exchange == "fused":
             return lin.forward_fused(q, s, torch.bfloat16)
         mine = slots[rank]
         runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=mine)
         dist.all_gather_into_tensor(slots.view(-1), mine.view(-1))
-        full.view(M, world, n_local).copy_(slots.permute(1, 0, 2))
-        return full
+        out = fulls[turn[0]]
+        turn[0] ^= 1
+        out.view(M, world, n_local).copy_(slots.permute(1, 0, 2))
+        return out
 
     def barrier():
         if world > 1:
@@ -311,13 +317,29 @@ def main_ours(args):
 
     # ---- end-to-end through the public API with HOST buffers (pinned): H2D of the activations,
     #      quantise + GEMM (+ gather), D2H of the result, every step
+    #      The result read-back of step i runs on a second stream and overlaps the upload and
+    #      the math of step i + 1 (PCIe is full duplex); buffers alternate and are guarded by events.
     host_a = [a.cpu().pin_memory() for a in a_sets]
-    host_c = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
-    dev_a = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    host_c = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_a = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    d2h_stream = torch.cuda.Stream()
+    d2h_done = [None, None]
 
     def e2e_step(i):
-        dev_a.copy_(host_a[i % 2], non_blocking=True)
-        host_c.copy_(step(dev_a), non_blocking=True)
+        b = i % 2
+        comp = torch.cuda.current_stream()
+        if d2h_done[b] is not None:
+            comp.wait_event(d2h_done[b])       # the result buffer about to be rewritten has been read back
+        dev_a[b].copy_(host_a[b], non_blocking=True)
+        out = step(dev_a[b])
+        ready = torch.cuda.Event()
+        ready.record(comp)
+        d2h_stream.wait_event(ready)
+        with torch.cuda.stream(d2h_stream):
+            host_c[b].copy_(out, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(d2h_stream)
+        d2h_done[b] = done
 
     e2e_steps = max(2, min(steps, 10))
     for i in range(2):
@@ -327,13 +349,14 @@ def main_ours(args):
     f0.record()
     for i in range(e2e_steps):
         e2e_step(i)
+    torch.cuda.current_stream().wait_stream(d2h_stream)   # the last read-backs are inside the timed region
     f1.record()
     barrier()
     e2e_ms_total = f0.elapsed_time(f1)
 
     # ---- dominant kernel alone (the GEMM launch of one step), CUDA events on its stream
     q, s = pkg.fp8_act_quant(a_sets[0])
-    gemm_out = full if world == 1 else slots[rank]
+    gemm_out = fulls[0] if world == 1 else slots[rank]
     for _ in range(3):
         runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=gemm_out)
     torch.cuda.synchronize()
@@ -381,7 +404,7 @@ def main_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                     "steps": e2e_steps, "ms_per_step": e2e_ms_total / e2e_steps,
-                    "note": "pinned host activations in, full [M,N] bf16 result out on every rank; the quantised weight is a resident parameter"},
+                    "note": "pinned host activations in, full [M,N] bf16 result out on every rank, every step; read-back of step i overlaps upload + math of step i+1 (second stream); the quantised weight is a resident parameter"},
             "gpu_launches": steps * 2,
             "roofline": {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp8_peak, "traffic": traffic,

@@ -186,10 +186,13 @@ int64_t tile_workspace_bytes(int64_t M, int64_t K) {
   return tile_ast_bytes(M, K) + (M < 16 ? 16 * align_up(K, 16) : 0);
 }
 
-// tile stream-K (128x256 tiles, M <= 256): groups of num_m CTAs share the (N tile, K block) units
+// 128x256 tiles with the last, partly empty wave split along K (B200FP8_VARIANT_TILE256_SK)
 struct TileSkPlan {
   int num_m, num_n, num_kb;
-  int groups;             // 0 when the shape cannot use this mode
+  int full;      // tiles handed out whole, round-robin
+  int tail;      // remaining tiles (< grid)
+  int split;     // K ranges per tail tile; < 2 means the shape gains nothing and runs as plain tiles
+  int kb_per;    // K blocks per range
   int64_t grid;
   int64_t ast_bytes, partial_bytes;
 };
@@ -199,13 +202,16 @@ TileSkPlan tile_sk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
   p.num_m = static_cast<int>((M + 127) / 128);
   p.num_n = static_cast<int>((N + 255) / 256);
   p.num_kb = static_cast<int>((K + 127) / 128);
-  const int64_t total = static_cast<int64_t>(p.num_n) * p.num_kb;
-  int64_t groups = p.num_m > 0 ? sm_count / p.num_m : 0;
-  if (groups > total) groups = total;
-  p.groups = (M > 256 || groups < 1) ? 0 : static_cast<int>(groups);
-  p.grid = static_cast<int64_t>(p.groups) * p.num_m;
+  const int64_t tiles = static_cast<int64_t>(p.num_m) * p.num_n;
+  p.grid = sm_count;
+  p.full = static_cast<int>((tiles / sm_count) * sm_count);
+  p.tail = static_cast<int>(tiles - p.full);
+  p.split = p.tail > 0 ? sm_count / p.tail : 1;
+  if (p.split > p.num_kb / 4) p.split = p.num_kb / 4;   // keep ranges of at least 4 K blocks
+  if (p.split < 1) p.split = 1;
+  p.kb_per = (p.num_kb + p.split - 1) / p.split;
   p.ast_bytes = tile_workspace_bytes(M, K);
-  p.partial_bytes = 2 * p.grid * 128 * 256 * 4;
+  p.partial_bytes = p.split >= 2 ? static_cast<int64_t>(p.tail) * p.split * 128 * 256 * 4 : 0;
   return p;
 }
 
@@ -218,14 +224,20 @@ double wave_efficiency(int64_t tiles, int sms) {
 int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
   // Decode shapes (M <= 256) are weight-streaming and HBM-bound. Measured on B200 at N = 28672,
   // K = 8192: the plain 128x256 tile kernel (46 us at M = 16, 5.1 TB/s with 112 of 148 SMs busy)
-  // beats both stream-K forms (swap-AB 65 us; K-split tiles 58 us including their fix-up pass),
-  // so AUTO never picks those; they stay selectable by name.
+  // beats the swap-AB stream-K kernel (65 us), so AUTO does not pick that one.
   if (M <= 256) return (N > 128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
   const int64_t num_m = (M + 127) / 128;
   const double e128 = wave_efficiency(num_m * ((N + 127) / 128), sm_count);
   const double e256 = wave_efficiency(num_m * ((N + 255) / 256), sm_count);
   // the 128x256 tile moves 25 % fewer operand bytes per flop; prefer it unless the last wave is much emptier
-  return (e256 * 1.15 >= e128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
+  if (e256 * 1.15 < e128) return B200FP8_VARIANT_TILE128;
+  // A mostly empty last wave is worth splitting along K, but the split-K kernel runs its
+  // whole-tile part about 5 % slower (measured) and adds a fix-up pass: only take it when the
+  // idle share of the last wave is at least a tenth of the whole run.
+  const TileSkPlan p = tile_sk_plan(M, N, K, sm_count);
+  const int64_t waves = (static_cast<int64_t>(p.num_m) * p.num_n + sm_count - 1) / sm_count;
+  const bool worth = p.split >= 2 && (1.0 - 1.0 / p.split) >= 0.10 * static_cast<double>(waves);
+  return worth ? B200FP8_VARIANT_TILE256_SK : B200FP8_VARIANT_TILE256;
 }
 
 template <int BN>
@@ -250,7 +262,7 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t err;
-  if (BN == 256 && args.sk_groups > 0) {
+  if (BN == 256 && args.sk_split >= 2) {
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, true>, ta, tb, args);
   } else if (args.n_dst > 1) {
@@ -367,7 +379,6 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return tile_workspace_bytes(M, K);
   if (variant == B200FP8_VARIANT_TILE256_SK) {
-    if (M > 256) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
     if (M == 0 || N == 0 || K == 0) return 0;
     const TileSkPlan p = tile_sk_plan(M, N, K, sms);
     return p.ast_bytes + p.partial_bytes;
@@ -430,63 +441,29 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
+  if (n_dst > 1 && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
   if (n_dst > 1 && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
 
+  TileSkPlan skp = {};
   if (variant == B200FP8_VARIANT_TILE256_SK) {
-    if (M > 256) return B200FP8_ERR_VARIANT;
-    const TileSkPlan p = tile_sk_plan(M, N, K, dev->sm_count);
-    if (p.groups < 1) return B200FP8_ERR_VARIANT;
-    if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < p.ast_bytes + p.partial_bytes)
-      return B200FP8_ERR_WORKSPACE;
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
-    GemmArgs args;
-    fill_dst(args);
-    uint8_t* a_pad = M < 16 ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
-    args.a_from_prep = a_pad != nullptr;
-    args.sk_groups = p.groups;
-    args.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + p.ast_bytes);
-    args.AsT = static_cast<const float*>(workspace);
-    args.m_pad = align_up(M, 128);
-    {
-      const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
-      tile_prep_kernel<<<dim3(grid.x, grid.y, a_pad != nullptr ? 2u : 1u), 256, 0, stream>>>(
-          As, static_cast<float*>(workspace), M, args.m_pad, static_cast<int>(kblocks), ld_as,
-          static_cast<const uint8_t*>(A), a_pad, K, lda, align_up(K, 16));
-      st = launch_status();
-      if (st != B200FP8_OK) return st;
-    }
-    args.As = As;
-    args.Bs = Bs;
-    args.C = C;
-    args.M = M;
-    args.N = N;
-    args.K = K;
-    args.ld_as = ld_as;
-    args.ld_bs = ld_bs;
-    args.ldc = ldc;
-    args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
-    args.status_word = status_word;
-#ifdef B200FP8_TRACE
-    args.trace = nullptr;
-#endif
-    st = launch_tile<256>(a_pad ? a_pad : A, B, args, a_pad ? align_up(K, 16) : lda, ldb, dev->sm_count, stream, p.grid);
-    if (st != B200FP8_OK) return st;
-    const dim3 fix_grid(static_cast<unsigned>(p.num_n * p.num_m), 16u);
-    tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, p.num_kb, ldc,
-                                                       out_dtype == B200FP8_OUT_FP32, 256, p.num_m, p.num_n, p.groups);
-    return launch_status();
+    skp = tile_sk_plan(M, N, K, dev->sm_count);
+    if (skp.split < 2) variant = B200FP8_VARIANT_TILE256;   // nothing to split: same as the plain tile kernel
   }
 
-  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) {
-    const int64_t need = tile_workspace_bytes(M, K);
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
+      variant == B200FP8_VARIANT_TILE256_SK) {
+    const bool sk = variant == B200FP8_VARIANT_TILE256_SK;
+    const int64_t need = tile_workspace_bytes(M, K) + (sk ? skp.partial_bytes : 0);
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
     fill_dst(args);
     uint8_t* a_pad = M < 16 ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
     args.a_from_prep = a_pad != nullptr;
-    args.sk_groups = 0;
-    args.partial = nullptr;
+    args.sk_full = sk ? skp.full : 0;
+    args.sk_split = sk ? skp.split : 0;
+    args.sk_kb_per = sk ? skp.kb_per : 0;
+    args.partial = sk ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tile_workspace_bytes(M, K)) : nullptr;
     args.AsT = static_cast<const float*>(workspace);
     args.m_pad = align_up(M, 128);
     {
@@ -513,6 +490,15 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
 #endif
     const void* a_eff = a_pad ? static_cast<const void*>(a_pad) : A;
     const int64_t lda_eff = a_pad ? align_up(K, 16) : lda;
+    if (sk) {
+      st = launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream, skp.grid);
+      if (st != B200FP8_OK) return st;
+      const dim3 fix_grid(static_cast<unsigned>(skp.tail), 16u);
+      tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, skp.num_kb, ldc,
+                                                         out_dtype == B200FP8_OUT_FP32, 256, skp.num_m, skp.num_n,
+                                                         skp.full, skp.split, skp.kb_per);
+      return launch_status();
+    }
     return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream)
                                               : launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream);
   }

@@ -45,13 +45,13 @@ __host__ __device__ __forceinline__ int64_t streamk_owner(int64_t u, int64_t tot
 }
 
 struct GemmArgs {
-  // Stream-K mode (sk_groups > 0, used when M spans at most a few 128-row blocks): the
-  // (N tile, K block) units are split evenly over sk_groups groups of num_m CTAs; CTA c
-  // works on M block c % num_m of group c / num_m, so that the CTAs of a group stream the
-  // same weight tiles at the same time and every SM gets the same share of the weight.
-  // Segments that do not cover a whole K range go to `partial` as fp32 [slot][128][BN],
-  // slot = 2 * cta + (0 for the CTA's first segment, 1 for a later one).
-  int sk_groups;
+  // Tail split-K (kernels instantiated with SK = true): tiles [0, sk_full) are handed out
+  // round-robin as whole tiles; the remaining R < grid tiles - the last, partly empty wave -
+  // are each cut into sk_split K ranges of sk_kb_per K blocks, one range per CTA, so that the
+  // tail takes 1 / sk_split of a tile time. CTA c < R * sk_split works on tile sk_full + c /
+  // sk_split, range c % sk_split, and leaves its fp32 partial sums in `partial` as
+  // [c][128][BN]; tile_sk_fixup_kernel adds the ranges of each tail tile in a fixed order.
+  int sk_full, sk_split, sk_kb_per;
   float* partial;
   // Destinations of the result: dst[0] is C itself; dst[1..n_dst-1] are further buffers that
   // receive the same [M, N] block (other GPUs' output buffers mapped into this process, for
@@ -137,59 +137,68 @@ struct Segment {
 };
 
 struct SegCursor {
-  int tile;         // tile mode: next tile index
-  int64_t u, u1;    // stream-K mode: remaining units [u, u1) of this CTA's group
+  int tile;          // next whole tile of the round-robin part
+  bool tail_done;    // the tail range of this CTA (SK kernels) has been handed out
   bool started;
 };
 
 template <bool SK>
-__device__ __forceinline__ SegCursor seg_begin(int sk_groups, int num_m, int num_n, int num_kb) {
+__device__ __forceinline__ SegCursor seg_begin() {
   SegCursor c;
   c.tile = static_cast<int>(blockIdx.x);
+  c.tail_done = false;
   c.started = false;
-  c.u = c.u1 = 0;
-  if constexpr (SK) {
-    const int64_t total = static_cast<int64_t>(num_n) * num_kb;
-    const int64_t g = blockIdx.x / num_m;
-    c.u = streamk_first_unit(g, total, sk_groups);
-    c.u1 = streamk_first_unit(g + 1, total, sk_groups);
-  }
   return c;
+}
+
+// The tail range of this CTA: false if it has none.
+__device__ __forceinline__ bool seg_tail(const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles, Segment& s) {
+  const int u = static_cast<int>(blockIdx.x);
+  const int tail_tiles = num_tiles - a.sk_full;
+  if (u >= tail_tiles * a.sk_split) return false;
+  const int t = a.sk_full + u / a.sk_split;
+  const int piece = u - (u / a.sk_split) * a.sk_split;
+  tile_coords(t, num_m, num_n, s.m_blk, s.n_blk);
+  s.kb_begin = piece * a.sk_kb_per;
+  s.kb_end = s.kb_begin + a.sk_kb_per < num_kb ? s.kb_begin + a.sk_kb_per : num_kb;
+  return s.kb_begin < s.kb_end;
 }
 
 // Number of K blocks this CTA processes in total.
 template <bool SK>
-__device__ __forceinline__ uint32_t seg_total_kblocks(const SegCursor& c, int sk_groups, int num_tiles, int num_kb) {
-  (void)sk_groups;
-  if constexpr (SK) return static_cast<uint32_t>(c.u1 - c.u);
-  const int mine = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                   static_cast<int>(gridDim.x);
-  return static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
+__device__ __forceinline__ uint32_t seg_total_kblocks(const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles) {
+  const int whole_end = SK ? a.sk_full : num_tiles;
+  int mine = 0;
+  if (static_cast<int>(blockIdx.x) < whole_end)
+    mine = (whole_end - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  uint32_t total = static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
+  if constexpr (SK) {
+    Segment s;
+    if (seg_tail(a, num_m, num_n, num_kb, num_tiles, s)) total += static_cast<uint32_t>(s.kb_end - s.kb_begin);
+  }
+  return total;
 }
 
 template <bool SK>
-__device__ __forceinline__ bool seg_next(SegCursor& c, int sk_groups, int num_m, int num_n, int num_kb, int num_tiles,
+__device__ __forceinline__ bool seg_next(SegCursor& c, const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles,
                                          Segment& s) {
-  (void)sk_groups;
   s.first = !c.started;
   c.started = true;
-  if constexpr (SK) {
-    if (c.u >= c.u1) return false;
-    s.m_blk = static_cast<int>(blockIdx.x % num_m);
-    s.n_blk = static_cast<int>(c.u / num_kb);
-    s.kb_begin = static_cast<int>(c.u - static_cast<int64_t>(s.n_blk) * num_kb);
-    const int64_t left = c.u1 - c.u;
-    s.kb_end = (num_kb - s.kb_begin) < left ? num_kb : s.kb_begin + static_cast<int>(left);
-    c.u += s.kb_end - s.kb_begin;
+  const int whole_end = SK ? a.sk_full : num_tiles;
+  if (c.tile < whole_end) {
+    tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
+    s.kb_begin = 0;
+    s.kb_end = num_kb;
+    c.tile += static_cast<int>(gridDim.x);
     return true;
-  } else {
-  if (c.tile >= num_tiles) return false;
-  tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
-  s.kb_begin = 0;
-  s.kb_end = num_kb;
-  c.tile += static_cast<int>(gridDim.x);
-  return true;
   }
+  if constexpr (SK) {
+    if (!c.tail_done) {
+      c.tail_done = true;
+      return seg_tail(a, num_m, num_n, num_kb, num_tiles, s);
+    }
+  }
+  return false;
 }
 
 // Tensor maps of the destinations of the multi-destination kernel: byte matrices
@@ -259,9 +268,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       if (args.a_from_prep) asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t it = 0;
       bool ok = true;
-      SegCursor cur = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
+      SegCursor cur = seg_begin<SK>();
       Segment seg;
-      while (ok && seg_next<SK>(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+      while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
         const int m0 = seg.m_blk * Cfg::BM;
         const int n0 = seg.n_blk * BN;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
@@ -303,8 +312,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     uint32_t it = 0;
     uint32_t last = 0xffffffffu;
     bool ok = true;
-    const SegCursor cur0 = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
-    const uint32_t total_it = seg_total_kblocks<SK>(cur0, args.sk_groups, num_tiles, num_kb);
+    const uint32_t total_it = seg_total_kblocks<SK>(args, num_m, num_n, num_kb, num_tiles);
     {
       for (; it < total_it; ++it) {
         if ((it & 1u) != p) continue;
@@ -360,9 +368,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     // the scale copy AsT is written by the preceding tile_prep_kernel; with programmatic
     // dependent launch this kernel may have started before that grid finished
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    SegCursor cur = seg_begin<SK>(args.sk_groups, num_m, num_n, num_kb);
+    SegCursor cur = seg_begin<SK>();
     Segment seg;
-    while (ok && seg_next<SK>(cur, args.sk_groups, num_m, num_n, num_kb, num_tiles, seg)) {
+    while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
       const int m0 = seg.m_blk * Cfg::BM;
       const int n0 = seg.n_blk * BN;
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
@@ -457,10 +465,10 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
 
 #define ACC(i) (((i) & 1) ? acc[(i) >> 5][((i) & 31) >> 1].y : acc[(i) >> 5][((i) & 31) >> 1].x)
       if (SK && (seg.kb_begin != 0 || seg.kb_end != num_kb)) {
-        // stream-K: this CTA saw only part of the K range - leave the fp32 partial sums of the
-        // rows that exist in the workspace; tile_sk_fixup_kernel adds the pieces of the tile
+        // tail split-K: this CTA saw only part of the K range - leave the fp32 partial sums of the
+        // rows that exist in the workspace; tile_sk_fixup_kernel adds the ranges of the tile
         if (row < M) {
-          const int64_t slot = 2 * static_cast<int64_t>(blockIdx.x) + (seg.first ? 0 : 1);
+          const int64_t slot = static_cast<int64_t>(blockIdx.x);
           float* prow = args.partial + (slot * Cfg::BM + (q * 32 + lane)) * BN + cw * Cfg::EPI_COLS;
 #pragma unroll
           for (int j = 0; j < Cfg::EPI_COLS; j += 4)
@@ -591,29 +599,23 @@ gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
 }
 
-// Stream-K mode: adds the fp32 pieces of every output tile whose K range was split between
-// groups, in ascending group order (fixed order: bit-reproducible), and writes C. Grid =
-// (num_n * num_m tiles, 16 row chunks of 8 rows); BN threads, one per tile column. Tiles
-// that one CTA covered completely were written by the GEMM kernel and are skipped.
+// Tail split-K: adds the K ranges of every tail tile (ascending range order: fixed, hence
+// bit-reproducible) and writes C. Grid = (tail tiles, 16 row chunks of 8 rows); BN threads,
+// one per tile column.
 __global__ void __launch_bounds__(256)
 tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
-                     int out_fp32, int BN, int num_m, int num_n, int sk_groups) {
-  const int n_blk = blockIdx.x / num_m;
-  const int m_blk = blockIdx.x - n_blk * num_m;
-  const int64_t total = static_cast<int64_t>(num_n) * num_kb;
-  const int64_t g_first = streamk_owner(static_cast<int64_t>(n_blk) * num_kb, total, sk_groups);
-  const int64_t g_last = streamk_owner(static_cast<int64_t>(n_blk) * num_kb + num_kb - 1, total, sk_groups);
-  if (g_first == g_last) return;
+                     int out_fp32, int BN, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per) {
+  int m_blk, n_blk;
+  tile_coords(sk_full + static_cast<int>(blockIdx.x), num_m, num_n, m_blk, n_blk);
   const int64_t col = static_cast<int64_t>(n_blk) * BN + threadIdx.x;
   if (static_cast<int>(threadIdx.x) >= BN || col >= N) return;
   const int r0 = blockIdx.y * 8;
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-  for (int64_t g = g_first; g <= g_last; ++g) {
-    const int64_t cta = g * num_m + m_blk;
-    const int64_t first_tile_of_g = streamk_first_unit(g, total, sk_groups) / num_kb;
-    const int64_t slot = 2 * cta + (first_tile_of_g == n_blk ? 0 : 1);
+  for (int j = 0; j < sk_split; ++j) {
+    if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
+    const int64_t slot = static_cast<int64_t>(blockIdx.x) * sk_split + j;
     const float* src = partial + (slot * 128 + r0) * BN + threadIdx.x;
 #pragma unroll
     for (int i = 0; i < 8; ++i)

@@ -54,7 +54,7 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_TILE128 1 /* persistent tcgen05 kernel, 128x128 output tiles */
 #define B200FP8_VARIANT_TILE256 2 /* persistent tcgen05 kernel, 128x256 output tiles */
 #define B200FP8_VARIANT_STREAMK 3 /* swap-AB stream-K kernel for M <= 256 (decode shapes) */
-#define B200FP8_VARIANT_TILE256_SK 4 /* 128x256 tile kernel with the K range of the tiles split evenly over all SMs, M <= 256 */
+#define B200FP8_VARIANT_TILE256_SK 4 /* 128x256 tiles; the tiles of the last, partly empty wave are split along K over the idle SMs */
 
 /* codes a kernel may leave in *status_word */
 #define B200FP8_DEV_OK 0u

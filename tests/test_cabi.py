@@ -74,7 +74,9 @@ def test_workspace_and_variant_queries(lib):
     ast = 64 * 4096 * 4                                       # K-block-major copy of As: [K/128][M] fp32
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T128) == ast
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, T256) == ast
-    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, AUTO) == ast
+    # 512 tiles on 148 SMs: 444 whole tiles + 68 tail tiles cut into 2 K ranges each (fp32 partial tiles)
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 4) == ast + 68 * 2 * 128 * 256 * 4
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, AUTO) in (ast, ast + 68 * 2 * 128 * 256 * 4)
     assert lib.b200fp8_gemm_workspace_bytes(300, 512, 200, T128) == 2 * 384 * 4   # M padded to 128, K blocks rounded up
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, SK) == -5     # M > 256 cannot use stream-K
     assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, 42) == -5
@@ -89,10 +91,9 @@ def test_workspace_and_variant_queries(lib):
     assert lib.b200fp8_gemm_pick_variant(1, 28672, 8192) == T256     # decode shapes: plain tile kernel measured fastest
     assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == T256
     assert lib.b200fp8_gemm_pick_variant(16, 128, 512) == T128
-    assert lib.b200fp8_gemm_workspace_bytes(300, 28672, 8192, TSK) == -5     # M > 256
-    g = 148 // 1
-    assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4 + 2 * g * 128 * 256 * 4
-    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256)
+    # 112 tiles on 148 SMs: the tail cannot be split in two, the variant degenerates to plain tiles
+    assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4
+    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256, 4)
 
 
 @pytest.mark.parametrize("tiles,num_kb,grid", [(224, 64, 148), (8, 8, 148), (3, 5, 4), (1, 1, 1), (7, 3, 5),
