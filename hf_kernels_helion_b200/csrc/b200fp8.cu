@@ -336,6 +336,14 @@ int b200fp8_quant_act(const void* x, void* q, float* s, int64_t M, int64_t K, in
   int st = device_info(&dev);
   if (st != B200FP8_OK) return st;
   const int64_t groups = M * ((K + 127) / 128);
+  if (K % 128 == 0 && (M == 1 || (ldx == K && ldq == K && lds == K / 128)) &&
+      (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && groups <= (int64_t{1} << 35)) {
+    // one unbroken run of 128-element groups: no row / column arithmetic in the kernel
+    const int64_t blocks = (groups + 31) / 32;
+    quant_act_contig_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x), static_cast<uint4*>(q), s, groups);
+    return launch_status();
+  }
   const int64_t blocks_needed = (groups * 8 + 255) / 256;
   const int64_t max_blocks = static_cast<int64_t>(dev->sm_count) * 32;
   const int grid = static_cast<int>(blocks_needed < max_blocks ? blocks_needed : max_blocks);

@@ -33,34 +33,47 @@ __device__ __forceinline__ float amax8(const uint4& v) {
 }
 
 // e4m3(x / scale) without a division per element, bit-identical to the division.
-// q = x * rcp (rcp = 1 / scale, correctly rounded) is within 2 ulp of the IEEE quotient, so
-// the e4m3 cast of the two can differ only if an e4m3 rounding boundary lies between them:
-//   - q within a few ulp of a tie of the normal e4m3 range, i.e. the 20 fp32 mantissa bits
-//     below the three kept ones are about 0x80000;
-//   - 0 < |q| < 2^-6 (the e4m3 subnormal range has its ties elsewhere).
-// Both conditions are folded into two running unsigned minima over the elements a thread
-// converts; if either fires (rare), the thread redoes its elements with the true division.
-// (|q| cannot leave the range upwards since |x| <= amax; a scale so small that 1 / scale
-// overflows is sent to the division path as a whole.)
-struct ExactnessProbe {
-  uint32_t tie_min = 0xFFFFFFFFu;   // min over elements of (bits & 0xFFFFF) - (0x80000 - 8); <= 16 means "near a tie"
-  uint32_t low_min = 0xFFFFFFFFu;   // min over elements of |q| bits - 1; < 0x3C800000 - 1 means "0 < |q| < 2^-6"
-  __device__ __forceinline__ float mul(float x, float rcp) {
-    const float q = x * rcp;
-    const uint32_t bits = __float_as_uint(q);
-    tie_min = min(tie_min, (bits & 0xFFFFFu) - (0x80000u - 8u));
-    low_min = min(low_min, (bits & 0x7FFFFFFFu) - 1u);
-    return q;
-  }
-  __device__ __forceinline__ bool inexact() const { return tie_min <= 16u || low_min < 0x3C800000u - 1u; }
-};
+// With y = RN(1 / scale) (one correctly rounded reciprocal per group):
+//     q0 = x * y            within an ulp of the quotient
+//     r  = fma(-scale, q0, x)   the exact remainder
+//     q  = fma(r, y, q0)    = RN(x / scale)          (Markstein's correction step)
+// as long as nothing leaves the normal fp32 range where it matters. bf16 inputs have 8-bit
+// mantissas and scale = amax / 448 with amax one of them, so the claim involves only
+// 128 x 128 mantissa pairs; the tests run every pair through the kernel against the division.
+// Range: |q| <= 448 always (|x| <= amax). Quotients below 2^-10 become e4m3 zero whatever their
+// low bits; for |q| >= 2^-11 the remainder's last bit is >= scale * 2^-57, normal when
+// scale >= 2^-60. Smaller scales (and infinite / NaN ones) take the true division.
+// The sign of x is copied onto the result so that -0 stays -0 (the remainder of an exact
+// zero is +0 and would otherwise absorb the sign).
+constexpr float kScaleMinFast = 8.6736174e-19f;   // 2^-60
+constexpr float kScaleMaxFast = 1.0e37f;          // every finite bf16 amax / 448 is below this
 
-__device__ __forceinline__ uint2 quant8_fast(const uint4& v, float rcp, ExactnessProbe& pr) {
+__device__ __forceinline__ float div_by_scale(float x, float scale, float y) {
+  const float q0 = x * y;
+  const float r = __fmaf_rn(-scale, q0, x);
+  const float q = __fmaf_rn(r, y, q0);
+  return __uint_as_float((__float_as_uint(q) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
+}
+
+// amax / 448 by the same correction step with the constant y = RN(1 / 448); exact for every
+// bf16 amax whose quotient is a normal number (checked over all of them by the tests), true
+// division otherwise.
+__device__ __forceinline__ float scale_of_amax(float amax) {
+  if (amax >= 1.0e-30f && amax <= 3.4e38f) {
+    constexpr float y448 = 1.0f / 448.0f;
+    const float q0 = amax * y448;
+    const float r = __fmaf_rn(-448.0f, q0, amax);
+    return __fmaf_rn(r, y448, q0);
+  }
+  return __fdiv_rn(amax, 448.0f);
+}
+
+__device__ __forceinline__ uint2 quant8_fast(const uint4& v, float scale, float y) {
   uint2 o;
-  o.x = cvt_e4m3x2(pr.mul(bf16_lo(v.x), rcp), pr.mul(bf16_hi(v.x), rcp)) |
-        (cvt_e4m3x2(pr.mul(bf16_lo(v.y), rcp), pr.mul(bf16_hi(v.y), rcp)) << 16);
-  o.y = cvt_e4m3x2(pr.mul(bf16_lo(v.z), rcp), pr.mul(bf16_hi(v.z), rcp)) |
-        (cvt_e4m3x2(pr.mul(bf16_lo(v.w), rcp), pr.mul(bf16_hi(v.w), rcp)) << 16);
+  o.x = cvt_e4m3x2(div_by_scale(bf16_lo(v.x), scale, y), div_by_scale(bf16_hi(v.x), scale, y)) |
+        (cvt_e4m3x2(div_by_scale(bf16_lo(v.y), scale, y), div_by_scale(bf16_hi(v.y), scale, y)) << 16);
+  o.y = cvt_e4m3x2(div_by_scale(bf16_lo(v.z), scale, y), div_by_scale(bf16_hi(v.z), scale, y)) |
+        (cvt_e4m3x2(div_by_scale(bf16_lo(v.w), scale, y), div_by_scale(bf16_hi(v.w), scale, y)) << 16);
   return o;
 }
 
@@ -77,22 +90,46 @@ __device__ __forceinline__ uint2 quant8_div(const uint4& v, float scale) {
 // scale == 0 (all-zero group) yields zero bytes instead of the 0/0 NaN of the formula.
 template <int NV>
 __device__ __forceinline__ void quant_vecs(const uint4 (&v)[NV], float scale, uint2 (&o)[NV]) {
-  if (scale == 0.f) {
+  if (scale >= kScaleMinFast && scale <= kScaleMaxFast) {
+    const float y = __frcp_rn(scale);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[i] = quant8_fast(v[i], scale, y);
+  } else if (scale == 0.f) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) o[i] = make_uint2(0u, 0u);
-    return;
-  }
-  bool exact_path = scale < 1.0e-30f;   // 1 / scale would overflow or lose bits: divide
-  if (!exact_path) {
-    const float rcp = __frcp_rn(scale);
-    ExactnessProbe pr;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) o[i] = quant8_fast(v[i], rcp, pr);
-    exact_path = pr.inexact();
-  }
-  if (exact_path) {
+  } else {
 #pragma unroll
     for (int i = 0; i < NV; ++i) o[i] = quant8_div(v[i], scale);
+  }
+}
+
+// Contiguous case (K a multiple of 128, rows packed back to back in x, q and s): the matrix
+// is one run of 128-element groups, thread t owns elements [16 t, 16 t + 16) and needs no
+// row / column arithmetic at all. Eight consecutive threads share a group; the host rounds the
+// grid up so that whole warps are inside or outside (four groups per warp).
+__global__ void __launch_bounds__(256)
+quant_act_contig_kernel(const uint4* __restrict__ x, uint4* __restrict__ q, float* __restrict__ s,
+                        int64_t total_groups) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t g = t >> 3;
+  const bool live = g < total_groups;
+  uint4 v[2];
+  v[0] = make_uint4(0u, 0u, 0u, 0u);
+  v[1] = make_uint4(0u, 0u, 0u, 0u);
+  if (live) {
+    v[0] = __ldg(x + 2 * t);
+    v[1] = __ldg(x + 2 * t + 1);
+  }
+  float amax = fmaxf(amax8(v[0]), amax8(v[1]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  const float scale = scale_of_amax(amax);
+  uint2 o[2];
+  quant_vecs<2>(v, scale, o);
+  if (live) {
+    q[t] = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
+    if ((threadIdx.x & 7) == 0) s[g] = scale;
   }
 }
 
@@ -139,7 +176,7 @@ quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, f
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-      const float scale = __fdiv_rn(amax, 448.0f);
+      const float scale = scale_of_amax(amax);
       uint8_t* dst = q + row[u] * ldq + col[u];
       if (has0[u]) {
         uint2 o[2];   // a missing second vector is zeros and is simply not stored
@@ -186,7 +223,7 @@ quant_weight_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q
   amax = warp_max[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
-  const float scale = __fdiv_rn(amax, 448.0f);
+  const float scale = scale_of_amax(amax);
   uint2 o[8];
   quant_vecs<8>(v, scale, o);
 #pragma unroll

@@ -58,6 +58,49 @@ def test_act_quant_every_bf16_value(device):
         _assert_bit_exact(q, s, q_ref, s_ref)
 
 
+def _bf16_from(exp, mant):
+    """bf16 values 2^exp * (1 + mant / 128) for integer tensors exp (unbiased) and mant (0..127)."""
+    bits = ((exp + 127) << 7) | mant
+    return bits.to(torch.int16).view(torch.bfloat16)
+
+
+def test_act_quant_all_mantissa_pairs(device):
+    """The kernel divides through a reciprocal and one remainder correction. Whether that equals
+    the IEEE division depends only on the mantissas of x and of the group maximum, so every
+    (x mantissa, amax mantissa) pair is run, both signs, at quotient exponents down to the
+    e4m3 flush range, and at group maxima from below the reciprocal path's lower limit to the
+    largest bf16 value."""
+    mant = torch.arange(128, dtype=torch.int32)
+    for amax_exp in (-70, -52, -51, -30, -3, 0, 7, 60, 127):
+        rel = torch.arange(0, -21, -1, dtype=torch.int32)                    # x exponent relative to amax
+        x_exp = (amax_exp + rel).clamp(min=-126)
+        xs = _bf16_from(x_exp[:, None].expand(-1, 128), mant[None, :].expand(21, -1)).reshape(-1)   # 2688 values
+        xs = torch.cat([xs, -xs])
+        rows = []
+        for am in range(128):
+            top = _bf16_from(torch.tensor([amax_exp], dtype=torch.int32), torch.tensor([am], dtype=torch.int32))
+            body = xs[xs.float().abs() <= top.float()]
+            pad = (-body.numel()) % 127
+            body = torch.cat([body, torch.zeros(pad, dtype=torch.bfloat16)]).view(-1, 127)
+            rows.append(torch.cat([body, top.expand(body.shape[0], 1)], dim=1))
+        x = torch.cat(rows, dim=0).contiguous()
+        q_ref, s_ref = oracle.quant_act(x)
+        q, s = pkg.fp8_act_quant(x.to(device))
+        _assert_bit_exact(q, s, q_ref, s_ref)
+
+
+def test_act_quant_scale_of_every_amax(device):
+    """scale = amax / 448 for every positive finite bf16 amax, subnormal ones included."""
+    bits = torch.arange(1, 0x7F80, dtype=torch.int32).to(torch.int16)
+    amax = bits.view(torch.bfloat16)
+    x = torch.zeros(amax.numel(), 128, dtype=torch.bfloat16)
+    x[:, 5] = amax
+    x[:, 77] = -amax
+    q_ref, s_ref = oracle.quant_act(x)
+    q, s = pkg.fp8_act_quant(x.to(device))
+    _assert_bit_exact(q, s, q_ref, s_ref)
+
+
 def test_act_quant_views_and_sentinels(device):
     """Row-strided input view; output written through the C ABI into a sentinel-filled
     buffer must leave every byte outside [M, K] untouched."""
