@@ -384,10 +384,11 @@ def main_ours(args):
         gemm_flops = 2.0 * M * n_local * K
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
         variant = _lib.load().b200fp8_gemm_pick_variant(M, n_local, K)
-        kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_kernel<256>", 3: "gemm_streamk_kernel"}[variant]
+        kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_kernel<256>", 3: "gemm_streamk_kernel",
+                  4: "gemm_tile_kernel<256> with tail split-K"}[variant]
         # DRAM traffic of one GEMM launch: ncu capture of the 1-GPU launch (profiles/), scaled by the
         # fraction of the weight and output this rank touches (A is read whole by every rank)
-        traffic_1gpu = {"read": 805.3e6, "write": 296.8e6}   # profiles/gemm_tile256_c5_8192x18432x7168.md
+        traffic_1gpu = {"read": 342.9e6, "write": 279.8e6}   # profiles/gemm_tile256_c5_8192x18432x7168.md
         traffic = None
         if traffic_1gpu is not None:
             traffic = (M * K + (traffic_1gpu["read"] - M * K) / world) + traffic_1gpu["write"] / world
