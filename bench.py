@@ -260,6 +260,18 @@ def main_ours(args):
     turn = [0]
 
     lin = tp.ShardedFp8Linear(B, Bs) if world > 1 else None
+    if world > 1 and args.exchange == "auto":
+        # measured on 2 and 4 GPUs: the per-GPU NVLink ingress bounds both fused forms, and the
+        # multicast form also receives its own slice back through the switch, so peer stores win
+        args.exchange = "fused"
+    elif world > 1 and args.exchange == "multimem":
+        # every rank must take the same path: agree on multicast support through an all-reduce
+        ok = torch.tensor([1.0 if tp.multicast_supported(dev) else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) <= 0:
+            raise SystemExit("--exchange multimem: this box reports no NVLink multicast support")
+    elif world == 1:
+        args.exchange = "none"
 
     def step(a_bf16):
         """One pass of the hot path on this rank; returns the contiguous [M, N] bf16 result."""
@@ -269,6 +281,8 @@ def main_ours(args):
             turn[0] ^= 1
             runtime.gemm(q, B, s, Bs, 128, 128, torch.bfloat16, out=out)
             return out
+        if args.exchange == "multimem":
+            return lin.forward_multimem(q, s, torch.bfloat16)
         if args.exchange == "fused":
             return lin.forward_fused(q, s, torch.bfloat16)
         mine = slots[rank]
@@ -320,7 +334,10 @@ def main_ours(args):
     #      The result read-back of step i runs on a second stream and overlaps the upload and
     #      the math of step i + 1 (PCIe is full duplex); buffers alternate and are guarded by events.
     host_a = [a.cpu().pin_memory() for a in a_sets]
-    host_c = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    # N > 1: every rank holds the whole [M, N] result; the host needs it once, so rank r reads back
+    # the row block [r M / world, (r + 1) M / world) and the ranks' host buffers together hold C
+    r0, r1 = rank * M // world, (rank + 1) * M // world
+    host_c = [torch.empty((r1 - r0, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     dev_a = [torch.empty((M, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     d2h_stream = torch.cuda.Stream()
     d2h_done = [None, None]
@@ -336,7 +353,7 @@ def main_ours(args):
         ready.record(comp)
         d2h_stream.wait_event(ready)
         with torch.cuda.stream(d2h_stream):
-            host_c[b].copy_(out, non_blocking=True)
+            host_c[b].copy_(out[r0:r1], non_blocking=True)
             done = torch.cuda.Event()
             done.record(d2h_stream)
         d2h_done[b] = done
@@ -399,13 +416,17 @@ def main_ours(args):
             "config": {"workload": WORKLOAD, "parallelism": f"N sharded over {world} GPU(s), exchange={args.exchange}" if world > 1 else "single GPU",
                        "step": "fp8_act_quant(A bf16) + w8a8_block_fp8_matmul" + (
                            "" if world == 1 else
+                           " whose epilogue writes the slice once to the NVLink multicast view of every GPU's [M,N] buffer (multimem.st, replicated by the NVSwitch) + 1-element all_reduce as barrier"
+                           if args.exchange == "multimem" else
                            " whose epilogue stores the slice into every GPU's [M,N] buffer over NVLink + 1-element all_reduce as barrier"
                            if args.exchange == "fused" else " + all_gather + slot->[M,N] copy"),
                        "l2": "per-step traffic (A bf16 117 MB rotating over 2 buffers, C bf16 302 MB) exceeds the 126 MB L2; no flush"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": world * M * K * 2, "d2h_bytes_per_step": M * N * 2,
                     "steps": e2e_steps, "ms_per_step": e2e_ms_total / e2e_steps,
-                    "note": "pinned host activations in, full [M,N] bf16 result out on every rank, every step; read-back of step i overlaps upload + math of step i+1 (second stream); the quantised weight is a resident parameter"},
+                    "note": "bytes are job totals: every rank uploads the whole pinned bf16 activation matrix (replicated input of the N-sharded layout), "
+                            "the [M,N] bf16 result goes back to pinned host memory once per step (each rank reads back its M/n_gpus row block of the assembled result); "
+                            "read-back of step i overlaps upload + math of step i+1 (second stream); the quantised weight is a resident parameter"},
             "gpu_launches": steps * 2,
             "roofline": {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp8_peak, "traffic": traffic,
@@ -431,8 +452,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
-                    help="N > 1: how the column slices reach every GPU (GEMM epilogue peer stores, or NCCL all-gather)")
+    ap.add_argument("--exchange", choices=["auto", "multimem", "fused", "nccl"], default="auto",
+                    help="N > 1: how the column slices reach every GPU: GEMM epilogue multicast stores through the "
+                         "NVSwitch, GEMM epilogue peer stores, or NCCL all-gather; auto = fused (fastest measured)")
     args = ap.parse_args()
     if args.impl == "reference":
         main_reference(args)

@@ -65,6 +65,10 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256, false>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<256>), TileCfg<256>::THREADS,
+              128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256, false>::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
@@ -265,6 +269,9 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   if (BN == 256 && args.sk_split >= 2) {
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, true>, ta, tb, args);
+  } else if (args.mc_store) {
+    cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_mc_kernel<BN>, ta, tb, args);
   } else if (args.n_dst > 1) {
     // one byte-matrix tensor map per destination: [M rows, N * element size], 32 x 128-byte boxes
     DstMaps dm;
@@ -398,8 +405,9 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
   return p.ast_bytes + p.partial_bytes;
 }
 
-// Shared body of b200fp8_gemm (n_dst = 1) and b200fp8_gemm_scatter (n_dst >= 1).
-static int gemm_impl(const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* dst,
+// Shared body of b200fp8_gemm (n_dst = 1), b200fp8_gemm_scatter (n_dst >= 1) and
+// b200fp8_gemm_multicast (n_dst = 1, mc = true: dst[0] is a multimem address).
+static int gemm_impl(bool mc, const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* dst,
                      const int64_t* dst_ld, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as,
                      int64_t ld_bs, int out_dtype, int variant, void* workspace, size_t workspace_bytes,
                      uint32_t* status_word, void* stream_) {
@@ -425,10 +433,12 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
   bool staged = (N * esize) % 16 == 0;
   for (int d = 0; d < n_dst; ++d)
     staged = staged && (reinterpret_cast<uintptr_t>(dst[d]) & 15u) == 0 && (dst_ld[d] * esize) % 16 == 0;
-  if (n_dst > 1 && !staged) return B200FP8_ERR_ALIGN;
+  if ((n_dst > 1 || mc) && !staged) return B200FP8_ERR_ALIGN;
+  if (mc && n_dst != 1) return B200FP8_ERR_SHAPE;
   auto fill_dst = [&](GemmArgs& a) {
     a.n_dst = n_dst;
     a.staged_store = staged ? 1 : 0;
+    a.mc_store = mc ? 1 : 0;
     for (int d = 0; d < 8; ++d) {
       a.dst[d] = d < n_dst ? dst[d] : nullptr;
       a.dst_ld[d] = d < n_dst ? dst_ld[d] : 0;
@@ -436,7 +446,7 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
   };
 
   if (K == 0) {
-    if (n_dst > 1) return B200FP8_ERR_SHAPE;
+    if (n_dst > 1 || mc) return B200FP8_ERR_SHAPE;
     gemm_zero_fill_kernel<<<dev->sm_count, 256, 0, stream>>>(C, M, N, ldc, out_dtype == B200FP8_OUT_FP32);
     return launch_status();
   }
@@ -449,8 +459,9 @@ static int gemm_impl(const void* A, const void* B, const float* As, const float*
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
-  if (n_dst > 1 && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
-  if (n_dst > 1 && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
+  const bool multi = n_dst > 1 || mc;
+  if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
+  if (multi && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
 
   TileSkPlan skp = {};
   if (variant == B200FP8_VARIANT_TILE256_SK) {
@@ -557,7 +568,17 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
                  int variant, void* workspace, size_t workspace_bytes, uint32_t* status_word, void* stream) {
   void* dst[1] = {C};
   const int64_t ld[1] = {ldc};
-  return gemm_impl(A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
+  return gemm_impl(false, A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
+                   workspace_bytes, status_word, stream);
+}
+
+int b200fp8_gemm_multicast(const void* A, const void* B, const float* As, const float* Bs, void* C_multimem,
+                           int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs,
+                           int64_t ldc, int out_dtype, int variant, void* workspace, size_t workspace_bytes,
+                           uint32_t* status_word, void* stream) {
+  void* dst[1] = {C_multimem};
+  const int64_t ld[1] = {ldc};
+  return gemm_impl(true, A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
                    workspace_bytes, status_word, stream);
 }
 
@@ -565,7 +586,7 @@ int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const fl
                          const int64_t* ldc_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                          int64_t ld_as, int64_t ld_bs, int out_dtype, int variant, void* workspace,
                          size_t workspace_bytes, uint32_t* status_word, void* stream) {
-  return gemm_impl(A, B, As, Bs, n_dst, C_dst, ldc_dst, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant,
+  return gemm_impl(false, A, B, As, Bs, n_dst, C_dst, ldc_dst, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant,
                    workspace, workspace_bytes, status_word, stream);
 }
 

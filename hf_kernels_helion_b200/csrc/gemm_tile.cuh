@@ -58,9 +58,13 @@ struct GemmArgs {
   // the N-sharded multi-GPU case). staged_store = 1 when every destination meets the TMA
   // rules (pointer and row pitch multiples of 16 bytes): the multi-destination kernel then
   // stages the tile in shared memory and sends it with asynchronous TMA stores.
+  // mc_store = 1: dst[0] is a multimem address of a buffer replicated on every GPU of a multicast
+  // group; the multi-destination kernel then re-reads each staged box row-wise and writes it
+  // with multimem.st, once, and the NVSwitch delivers it to all GPUs (this one included).
   int a_from_prep;   // 1: A was re-laid by tile_prep_kernel (M < 16 padded to 16 rows), the producer must wait for it
   int n_dst;
   int staged_store;
+  int mc_store;
   void* dst[8];
   int64_t dst_ld[8];
   const float* AsT;   // [ceil(K/128)][m_pad] token scales, K-block-major (written by tile_prep_kernel)
@@ -207,7 +211,9 @@ struct DstMaps {
   CUtensorMap m[8];
 };
 
-template <int BN, bool MULTI, bool SK>
+// MULTI: the result leaves through the shared-memory staging area; MC (with MULTI): by
+// multimem.st to a multicast address, otherwise by TMA stores to up to eight destinations.
+template <int BN, bool MULTI, bool SK, bool MC = false>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmArgs& args, const CUtensorMap* dmaps) {
   using Cfg = TileCfg<BN, MULTI>;
@@ -474,7 +480,61 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
           for (int j = 0; j < Cfg::EPI_COLS; j += 4)
             *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
         }
-      } else if (MULTI && args.staged_store) {
+      } else if (MULTI && MC) {
+        // Multicast destination: stage 128 bytes of each of the warp's 32 rows (same swizzle as
+        // below), then eight lanes per row read the row back as 16-byte chunks, so that every
+        // 128-byte row segment leaves as one contiguous multimem.st request.
+        uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
+        const int esize = args.out_fp32 ? 4 : 2;
+        const int passes = Cfg::EPI_COLS * esize / 128;
+        const int64_t n_bytes = N * esize;
+        uint8_t* mc_base = reinterpret_cast<uint8_t*>(args.dst[0]);
+        const int64_t ld_bytes = args.dst_ld[0] * esize;
+        for (int p = 0; p < passes; ++p) {
+          __syncwarp();                                // the previous pass has been read back
+          if (args.out_fp32) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              const int j0 = c * 4;
+#pragma unroll
+              for (int pp = 0; pp < Cfg::EPI_COLS / 32; ++pp)
+                if (pp == p) v4 = make_float4(ACC(pp * 32 + j0), ACC(pp * 32 + j0 + 1), ACC(pp * 32 + j0 + 2), ACC(pp * 32 + j0 + 3));
+              *reinterpret_cast<float4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = v4;
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint4 u = make_uint4(0u, 0u, 0u, 0u);
+              const int j0 = c * 8;
+#pragma unroll
+              for (int pp = 0; pp < Cfg::EPI_COLS / 64; ++pp)
+                if (pp == p) {
+                  __nv_bfloat162 v0 = __floats2bfloat162_rn(ACC(pp * 64 + j0), ACC(pp * 64 + j0 + 1));
+                  __nv_bfloat162 v1 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 2), ACC(pp * 64 + j0 + 3));
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 4), ACC(pp * 64 + j0 + 5));
+                  __nv_bfloat162 v3 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 6), ACC(pp * 64 + j0 + 7));
+                  u.x = *reinterpret_cast<uint32_t*>(&v0);
+                  u.y = *reinterpret_cast<uint32_t*>(&v1);
+                  u.z = *reinterpret_cast<uint32_t*>(&v2);
+                  u.w = *reinterpret_cast<uint32_t*>(&v3);
+                }
+              *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = u;
+            }
+          }
+          __syncwarp();
+          const int c = lane & 7;
+          const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + c * 16;
+          int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
+          uint8_t* gptr = mc_base + grow * ld_bytes + col_byte;
+          const bool col_ok = col_byte < n_bytes;
+#pragma unroll 2
+          for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
+            if (col_ok && grow < M) multimem_st_v4(gptr, v);
+          }
+        }
+      } else if (MULTI && !MC && args.staged_store) {
         // Full tile, multi-destination path: per pass, 128 bytes of each of this warp's 32 rows
         // go to the warp's staging area in the SWIZZLE_128B pattern (16-byte chunk index XOR
         // row % 8, conflict-free for the row-wise writes), and one TMA store per destination
@@ -572,7 +632,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   // ------------------------------------------------------------------ teardown
   if constexpr (MULTI) {
     // the output copies of this warp must be complete (written) before the CTA exits
-    if (warp >= 4 && lane == 0) bulk_wait_group0();
+    if (!MC && warp >= 4 && lane == 0) bulk_wait_group0();
+    if (MC && warp >= 4) __threadfence_system();   // multimem stores ordered before the kernel's end
   }
   __syncwarp();
   tc_fence_before();
@@ -597,6 +658,15 @@ __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
   gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
+}
+
+// Multicast form: args.dst[0] is a multimem address; every 128-byte row segment of a finished
+// tile is written once with multimem.st and replicated into all GPUs' buffers by the NVSwitch.
+template <int BN>
+__global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
+gemm_tile_mc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmArgs args) {
+  gemm_tile_body<BN, true, false, true>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Tail split-K: adds the K ranges of every tail tile (ascending range order: fixed, hence

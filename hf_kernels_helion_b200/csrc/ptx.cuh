@@ -179,6 +179,13 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // all committed groups of this thread have finished READING shared memory (it may be reused)
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // all committed groups of this thread are complete (their global writes are performed)
+// 16-byte store to a multimem (NVLink multicast) address: the switch replicates the write into
+// the memory of every GPU bound to the multicast object. The bits are not interpreted.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t policy_evict_first() {

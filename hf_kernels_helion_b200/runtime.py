@@ -173,6 +173,38 @@ def gemm_scatter(A, B, As, Bs, dst_ptrs, dst_lds, out_dtype: torch.dtype, varian
     _lib.check(st, "b200fp8_gemm_scatter")
 
 
+def gemm_multicast(A, B, As, Bs, mc_ptr: int, ldc: int, out_dtype: torch.dtype, variant=None) -> None:
+    """C = A @ B.T written through a multimem (NVLink multicast) address (b200fp8_gemm_multicast):
+    mc_ptr is the multicast view of a buffer that every GPU of the group holds, already offset to
+    the first element of this call's column slice; ldc is the buffer's row pitch in elements.
+    The NVSwitch replicates every store into all GPUs' copies (see MulticastBuffers in tp.py)."""
+    if out_dtype not in _OUT_CODES:
+        raise ValueError(f"output dtype must be torch.bfloat16 or torch.float32, got {out_dtype}")
+    _require_cuda(A, "A")
+    if not mc_ptr:
+        raise ValueError("mc_ptr is null: the group has no multicast mapping")
+    M, K = A.shape
+    N = B.shape[0]
+    if M == 0 or N == 0:
+        return
+    dev = A.device
+    lib = _lib.load()
+    A_, B_ = _row_major(A, 16), _row_major(B, 16)
+    As_, Bs_ = _row_major(As, 1), _row_major(Bs, 1)
+    v = resolve_variant(variant)
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200fp8_gemm_workspace_bytes(M, N, K, v))
+        if ws_bytes < 0:
+            _lib.check(-ws_bytes, "b200fp8_gemm_workspace_bytes")
+        ws = _workspace(dev, ws_bytes) if ws_bytes > 0 else None
+        st = lib.b200fp8_gemm_multicast(
+            A_.data_ptr(), B_.data_ptr(), As_.data_ptr(), Bs_.data_ptr(), int(mc_ptr),
+            M, N, K, _ld(A_), _ld(B_), _ld(As_), _ld(Bs_), int(ldc), _OUT_CODES[out_dtype], v,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "b200fp8_gemm_multicast")
+
+
 def _quant_common(x: torch.Tensor, name: str):
     if x.dim() != 2:
         raise ValueError(f"{name} must be 2-D, got shape {tuple(x.shape)}")

@@ -79,6 +79,42 @@ class PeerBuffers:
         self._bases = {}
 
 
+def multicast_supported(device: torch.device) -> bool:
+    """True when the CUDA driver reports NVLink multicast support for this device (what torch's
+    symmetric memory needs to hand out a multicast address)."""
+    try:
+        from torch._C._autograd import DeviceType
+        from torch._C._distributed_c10d import _SymmetricMemory
+        return bool(_SymmetricMemory.has_multicast_support(DeviceType.CUDA, device.index or 0))
+    except Exception:  # noqa: BLE001 - any failure of the probe means "do not use it"
+        return False
+
+
+class MulticastBuffers:
+    """One [M, N] output buffer per rank in torch symmetric memory, bound to an NVLink multicast
+    object: a store to `mc_ptr + offset` (multimem.st) lands at `offset` in EVERY rank's buffer,
+    replicated by the NVSwitch. `local` is this rank's copy as a tensor. Raises RuntimeError
+    where the group has no multicast support (mc_ptr would be 0)."""
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.local = symm_mem.empty((M, N), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group=self.group)
+        mc_base = int(self.handle.multicast_ptr)
+        if mc_base == 0:
+            raise RuntimeError("symmetric memory rendezvous gave no multicast address (NVLink multicast unsupported here)")
+        # the handle describes the allocation the tensor lives in: carry the tensor's offset over
+        rank = dist.get_rank(self.group)
+        offset = self.local.data_ptr() - int(self.handle.buffer_ptrs[rank])
+        nbytes = M * N * self.local.element_size()
+        if offset < 0 or offset + nbytes > int(self.handle.buffer_size):
+            raise RuntimeError("symmetric memory handle does not cover the tensor it was made for")
+        self.mc_ptr = mc_base + offset
+        dist.barrier(self.group)
+
+
 class ShardedFp8Linear:
     """Holds this rank's weight slice and runs  C = A . B^T  tensor-parallel.
 
@@ -173,6 +209,29 @@ class ShardedFp8Linear:
         if self.world > 1:
             dist.all_reduce(self._flag, group=self.group)
         return pb.local
+
+    def forward_multimem(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
+        """Contiguous C [M, N] on every rank, exchange fused into the GEMM through NVLink multicast:
+        the epilogue writes this rank's column slice ONCE to the multicast view of the [M, N]
+        buffers and the NVSwitch replicates it into every rank's copy, so a GPU sends N/world
+        columns instead of (world - 1) x that. One tiny all-reduce afterwards is the barrier.
+        Buffer alternation and lifetime of the returned tensor as for forward_fused."""
+        from . import runtime  # noqa: PLC0415
+
+        M = A.shape[0]
+        key = (M, output_dtype, A.device)
+        if getattr(self, "_mc_key", None) != key:
+            self._mc = [MulticastBuffers(M, self.N, output_dtype, A.device, self.group) for _ in range(2)]
+            self._mc_key = key
+            self._mc_turn = 0
+            self._mc_flag = torch.zeros(1, dtype=torch.float32, device=A.device)
+        mb = self._mc[self._mc_turn]
+        self._mc_turn ^= 1
+        col_bytes = self.rank * self.n_local * mb.local.element_size()
+        runtime.gemm_multicast(A, self.B, As, self.Bs, mb.mc_ptr + col_bytes, self.N, output_dtype)
+        if self.world > 1:
+            dist.all_reduce(self._mc_flag, group=self.group)
+        return mb.local
 
     def forward(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
         """Contiguous C [M, N] on every rank (all-gather, then one transpose copy of the slots)."""

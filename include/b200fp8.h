@@ -138,8 +138,9 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
  * separate all-gather pass is needed. C_dst[d] points at the first element of THIS call's
  * column slice inside destination d (a peer buffer opened with b200fp8_ipc_open, plus the
  * slice's column offset), ldc_dst[d] is that buffer's row pitch in elements.
- * Remote destinations are written with plain 16-byte stores over NVLink from a staged tile
- * (no TMA, no multicast). Every C_dst[d] must be 16-byte aligned, ldc_dst[d] and N multiples
+ * Each finished 32-row x 128-byte box is staged in shared memory and sent to every
+ * destination with an asynchronous TMA store (remote ones cross NVLink) while the following
+ * tiles compute; no TMA load ever touches peer memory. Every C_dst[d] must be 16-byte aligned, ldc_dst[d] and N multiples
  * of 16 bytes worth of elements; only the tile variants (or AUTO resolving to one) are
  * allowed. The stores are complete when the kernel is; the caller synchronises the GPUs
  * (stream order + a barrier between ranks) before any of them reads its buffer.
@@ -151,6 +152,24 @@ int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const fl
                          int out_dtype, int variant,
                          void* workspace, size_t workspace_bytes,
                          uint32_t* status_word, void* stream);
+
+/*
+ * b200fp8_gemm whose result goes to a multimem (NVLink multicast) address: C_multimem is the
+ * multicast view of one buffer that exists on every GPU of a multicast group (cuMulticast* /
+ * torch symmetric memory rendezvous), offset to the first element of THIS call's column
+ * slice; ldc is the buffer's row pitch in elements. Each 128-byte row segment of a finished
+ * tile is written once with multimem.st and the NVSwitch replicates it into all GPUs' copies,
+ * this GPU's included, so a GPU sends its slice once instead of once per peer. No counterpart
+ * in the reference. Same alignment rules, variants and completion semantics as
+ * b200fp8_gemm_scatter; the library cannot check that the address is a multimem address.
+ */
+int b200fp8_gemm_multicast(const void* A, const void* B, const float* As, const float* Bs,
+                           void* C_multimem,
+                           int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc,
+                           int out_dtype, int variant,
+                           void* workspace, size_t workspace_bytes,
+                           uint32_t* status_word, void* stream);
 
 /*
  * CUDA IPC helpers for b200fp8_gemm_scatter (no counterpart in the reference). export: a

@@ -39,7 +39,22 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             ok = ok and fused.shape == (M, N) and torch.equal(fused, out)
         runtime.check_device_status()
-        q.put((rank, bool(ok)))
+        # exchange through NVLink multicast (multimem.st, replicated by the NVSwitch), where the box has it;
+        # fp32 output as well, whose rows are 4-byte elements in 128-byte boxes
+        mc = torch.tensor([1.0 if tp.multicast_supported(dev) else 0.0], device=dev)
+        dist.all_reduce(mc, op=dist.ReduceOp.MIN)
+        used_mc = float(mc.item()) > 0
+        if used_mc:
+            for _ in range(3):
+                got = lin.forward_multimem(A.to(dev), As.to(dev), torch.bfloat16)
+                torch.cuda.synchronize()
+                ok = ok and got.shape == (M, N) and torch.equal(got, out)
+            got32 = lin.forward_multimem(A.to(dev), As.to(dev), torch.float32)
+            torch.cuda.synchronize()
+            ref32 = runtime.gemm(A.to(dev), B.to(dev), As.to(dev), Bs.to(dev), 128, 128, torch.float32)
+            ok = ok and torch.equal(got32, ref32)
+            runtime.check_device_status()
+        q.put((rank, (bool(ok), used_mc)))
     finally:
         dist.destroy_process_group()
 
@@ -57,4 +72,6 @@ def test_sharded_linear_nccl():
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    assert dict(q.get(timeout=5) for _ in range(world)) == {r: True for r in range(world)}
+    res = dict(q.get(timeout=5) for _ in range(world))
+    assert {r: v[0] for r, v in res.items()} == {r: True for r in range(world)}
+    print("multimem exchange exercised:", all(v[1] for v in res.values()))
