@@ -93,7 +93,12 @@ struct TileCfg {
   // 128 accumulators + 64 staging registers per epilogue thread do not fit the 168
   // registers a 384-thread CTA gets by default: the BN = 256 kernel moves registers
   // from the producer/MMA warpgroup to the two epilogue warpgroups with setmaxnreg.
-  static constexpr bool REBALANCE_REGS = (BN_ == 256);
+  // The BN = 128 kernel takes the same re-balancing (measured a few per cent faster with it).
+  // Starting the TMEM load of K block i + 1 before the FMAs of block i (a second staging set)
+  // was measured 15-20 % SLOWER for both tile widths: FMAs issued behind an outstanding
+  // tcgen05.ld of the same warp do not overlap it, so each warp simply loads, waits, multiplies,
+  // and the overlap comes from the other warp of the scheduler.
+  static constexpr bool REBALANCE_REGS = true;
   // setmaxnreg budget: the CTA is launched with 168 registers per thread (65536 / 384 rounded
   // down to a multiple of 8); the control warpgroup gives registers back, the two epilogue
   // warpgroups take them. setmaxnreg.inc BLOCKS until the registers exist, so the sum must
@@ -440,7 +445,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       // The scales AsT[kb][row] and Bs[nb, kb] come from global memory (L2 latency of several
       // hundred clocks). They are fetched a whole group of PF K blocks ahead so that their
       // first use never stalls the promotion loop.
-      constexpr int PF = 4;
+      constexpr int PF = (CHUNKS == 2) ? 2 : 4;
       float sa_c[PF], sb_c[PF], sa_n[PF], sb_n[PF];
       const int kb_last = seg.kb_end - 1;
 #pragma unroll
@@ -459,7 +464,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
-          if (ok && kb0 + j < seg.kb_end) ok = promote(sa_c[j] * sb_c[j]);
+          if (ok && kb0 + j < seg.kb_end) {
+            ok = promote(sa_c[j] * sb_c[j]);
+          }
         }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
