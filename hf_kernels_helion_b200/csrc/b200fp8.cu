@@ -190,6 +190,12 @@ int64_t tile_workspace_bytes(int64_t M, int64_t K) {
   return tile_ast_bytes(M, K) + (M < 16 ? 16 * align_up(K, 16) : 0);
 }
 
+// b200fp8_linear: scales K-block-major + the quantised activations (at least 16 rows, 16-byte row pitch)
+int64_t linear_prefix_bytes(int64_t M, int64_t K) {
+  if (M == 0 || K == 0) return 0;
+  return tile_ast_bytes(M, K) + align_up((M < 16 ? 16 : M) * align_up(K, 16), 256);
+}
+
 // 128x256 tiles with the last, partly empty wave split along K (B200FP8_VARIANT_TILE256_SK)
 struct TileSkPlan {
   int num_m, num_n, num_kb;
@@ -248,7 +254,8 @@ template <int BN>
 int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb, int sm_count,
                 cudaStream_t stream, int64_t sk_grid = 0) {
   CUtensorMap ta, tb;
-  int st = make_tmap_u8(&ta, A, args.a_from_prep ? 16 : args.M, args.K, lda, 128);
+  // the prep kernel's copy of A has at least 16 rows (M < 16 is zero-padded)
+  int st = make_tmap_u8(&ta, A, (args.a_from_prep && args.M < 16) ? 16 : args.M, args.K, lda, 128);
   if (st != B200FP8_OK) return st;
   st = make_tmap_u8(&tb, B, args.N, args.K, ldb, BN);
   if (st != B200FP8_OK) return st;
@@ -407,11 +414,19 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
 
 // Shared body of b200fp8_gemm (n_dst = 1), b200fp8_gemm_scatter (n_dst >= 1) and
 // b200fp8_gemm_multicast (n_dst = 1, mc = true: dst[0] is a multimem address).
+// x_bf16 != nullptr: the activations arrive unquantised (b200fp8_linear); A and As are then
+// produced by tile_prep_quant_kernel in the workspace.
+struct FusedQuant {
+  const void* x_bf16 = nullptr;
+  int64_t ldx = 0;
+};
+
 static int gemm_impl(bool mc, const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* dst,
                      const int64_t* dst_ld, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as,
                      int64_t ld_bs, int out_dtype, int variant, void* workspace, size_t workspace_bytes,
-                     uint32_t* status_word, void* stream_) {
+                     uint32_t* status_word, void* stream_, FusedQuant fq = FusedQuant()) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool fused_q = fq.x_bf16 != nullptr;
   if (n_dst < 1 || n_dst > 8 || dst == nullptr || dst_ld == nullptr) return B200FP8_ERR_SHAPE;
   void* C = dst[0];
   const int64_t ldc = dst_ld[0];
@@ -450,12 +465,20 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
     gemm_zero_fill_kernel<<<dev->sm_count, 256, 0, stream>>>(C, M, N, ldc, out_dtype == B200FP8_OUT_FP32);
     return launch_status();
   }
-  if (A == nullptr || B == nullptr || As == nullptr || Bs == nullptr) return B200FP8_ERR_NULL;
   const int64_t kblocks = (K + 127) / 128;
-  if (lda < K || ldb < K || ld_as < kblocks || ld_bs < kblocks) return B200FP8_ERR_SHAPE;
-  if (lda % 16 != 0 || ldb % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) != 0 ||
-      (reinterpret_cast<uintptr_t>(B) & 15u) != 0)
-    return B200FP8_ERR_ALIGN;
+  if (fused_q) {
+    if (B == nullptr || Bs == nullptr) return B200FP8_ERR_NULL;
+    if (K % 128 != 0 || fq.ldx < K || ldb < K || ld_bs < kblocks) return B200FP8_ERR_SHAPE;
+    if (fq.ldx % 8 != 0 || ldb % 16 != 0 || (reinterpret_cast<uintptr_t>(fq.x_bf16) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(B) & 15u) != 0)
+      return B200FP8_ERR_ALIGN;
+  } else {
+    if (A == nullptr || B == nullptr || As == nullptr || Bs == nullptr) return B200FP8_ERR_NULL;
+    if (lda < K || ldb < K || ld_as < kblocks || ld_bs < kblocks) return B200FP8_ERR_SHAPE;
+    if (lda % 16 != 0 || ldb % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(B) & 15u) != 0)
+      return B200FP8_ERR_ALIGN;
+  }
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
@@ -472,20 +495,31 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_TILE256_SK) {
     const bool sk = variant == B200FP8_VARIANT_TILE256_SK;
-    const int64_t need = tile_workspace_bytes(M, K) + (sk ? skp.partial_bytes : 0);
+    const int64_t prefix = fused_q ? linear_prefix_bytes(M, K) : tile_workspace_bytes(M, K);
+    const int64_t need = prefix + (sk ? skp.partial_bytes : 0);
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
     fill_dst(args);
-    uint8_t* a_pad = M < 16 ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
+    // the copy of A the prep kernel writes: the quantised activations (b200fp8_linear), or A
+    // zero-padded to 16 rows when M < 16
+    uint8_t* a_pad = (fused_q || M < 16) ? static_cast<uint8_t*>(workspace) + tile_ast_bytes(M, K) : nullptr;
     args.a_from_prep = a_pad != nullptr;
     args.sk_full = sk ? skp.full : 0;
     args.sk_split = sk ? skp.split : 0;
     args.sk_kb_per = sk ? skp.kb_per : 0;
-    args.partial = sk ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tile_workspace_bytes(M, K)) : nullptr;
+    args.partial = sk ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + prefix) : nullptr;
     args.AsT = static_cast<const float*>(workspace);
     args.m_pad = align_up(M, 128);
-    {
+    if (fused_q) {
+      const int64_t rows_q = M < 16 ? 16 : M;
+      const int64_t threads = args.m_pad * kblocks * 8;
+      tile_prep_quant_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(fq.x_bf16), fq.ldx, a_pad, align_up(K, 16), rows_q,
+          static_cast<float*>(workspace), M, args.m_pad, static_cast<int>(kblocks));
+      st = launch_status();
+      if (st != B200FP8_OK) return st;
+    } else {
       const dim3 grid(static_cast<unsigned>(args.m_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
       tile_prep_kernel<<<dim3(grid.x, grid.y, a_pad != nullptr ? 2u : 1u), 256, 0, stream>>>(
           As, static_cast<float*>(workspace), M, args.m_pad, static_cast<int>(kblocks), ld_as,
@@ -523,6 +557,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   }
 
   // stream-K decode variant
+  if (fused_q) return B200FP8_ERR_VARIANT;
   if (M > 256) return B200FP8_ERR_VARIANT;
   const StreamKPlan p = streamk_plan(M, N, K, dev->sm_count);
   if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < p.ast_bytes + p.partial_bytes)
@@ -570,6 +605,29 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   const int64_t ld[1] = {ldc};
   return gemm_impl(false, A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
                    workspace_bytes, status_word, stream);
+}
+
+int b200fp8_linear(const void* x_bf16, const void* B, const float* Bs, void* C, int64_t M, int64_t N, int64_t K,
+                   int64_t ldx, int64_t ldb, int64_t ld_bs, int64_t ldc, int out_dtype, int variant, void* workspace,
+                   size_t workspace_bytes, uint32_t* status_word, void* stream) {
+  if (x_bf16 == nullptr && M > 0 && K > 0) return B200FP8_ERR_NULL;
+  void* dst[1] = {C};
+  const int64_t ld[1] = {ldc};
+  FusedQuant fq;
+  fq.x_bf16 = x_bf16;
+  fq.ldx = ldx;
+  return gemm_impl(false, nullptr, B, nullptr, Bs, 1, dst, ld, M, N, K, 0, ldb, 0, ld_bs, out_dtype, variant, workspace,
+                   workspace_bytes, status_word, stream, fq);
+}
+
+int64_t b200fp8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
+  if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
+  if (M == 0 || N == 0 || K == 0) return 0;
+  const int sms = sm_count_or_default();
+  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return linear_prefix_bytes(M, K);
+  if (variant == B200FP8_VARIANT_TILE256_SK) return linear_prefix_bytes(M, K) + tile_sk_plan(M, N, K, sms).partial_bytes;
+  return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
 }
 
 int b200fp8_gemm_multicast(const void* A, const void* B, const float* As, const float* Bs, void* C_multimem,

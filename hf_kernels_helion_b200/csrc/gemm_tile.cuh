@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 
 #include "ptx.cuh"
+#include "quant.cuh"
 
 namespace b200fp8 {
 
@@ -674,6 +675,41 @@ __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_mc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs args) {
   gemm_tile_body<BN, true, false, true>(tmap_a, tmap_b, args, nullptr);
+}
+
+// Prep kernel of b200fp8_linear: quantises the bf16 activations (same arithmetic as
+// quant_act_contig_kernel, so the bytes and scales are identical to b200fp8_quant_act's) and
+// writes them where the GEMM kernel wants them: e4m3 rows into `Aq` (row pitch ldq, at least 16
+// rows, rows >= M zero) and the scales K-block-major into AsT[kb][m_pad] (rows >= M zero).
+// K is a multiple of 128. Eight threads per 128-element group; groups = m_pad x K/128.
+__global__ void __launch_bounds__(256)
+tile_prep_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __restrict__ Aq, int64_t ldq,
+                       int64_t rows_q, float* __restrict__ AsT, int64_t M, int64_t m_pad, int num_kb) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t g = t >> 3;
+  const int sub = threadIdx.x & 7;
+  const int64_t row = g / num_kb;                 // whole warps share a row quadruple: m_pad * num_kb is a multiple of 4
+  const int kg = static_cast<int>(g - row * num_kb);
+  if (row >= m_pad) return;
+  uint4 v[2];
+  v[0] = make_uint4(0u, 0u, 0u, 0u);
+  v[1] = make_uint4(0u, 0u, 0u, 0u);
+  if (row < M) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + row * ldx + kg * 128 + sub * 16);
+    v[0] = __ldg(src);
+    v[1] = __ldg(src + 1);
+  }
+  float amax = fmaxf(amax8(v[0]), amax8(v[1]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  const float scale = scale_of_amax(amax);
+  uint2 o[2];
+  quant_vecs<2>(v, scale, o);
+  if (row < rows_q)
+    *reinterpret_cast<uint4*>(Aq + row * ldq + kg * 128 + sub * 16) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
+  if (sub == 0) AsT[static_cast<int64_t>(kg) * m_pad + row] = scale;
 }
 
 // Tail split-K: adds the K ranges of every tail tile (ascending range order: fixed, hence

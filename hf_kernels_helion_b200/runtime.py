@@ -135,6 +135,55 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
     return out
 
 
+def linear(x, B, Bs, out_dtype: torch.dtype, variant=None, out=None) -> torch.Tensor:
+    """C = quantise(x) @ B.T in one library call (b200fp8_linear): x is bf16 [M, K] with K a
+    multiple of 128; the first launch quantises it per 1x128 group straight into the layout the
+    GEMM kernel reads, the GEMM follows. Bit-identical to quant_act() followed by gemm()."""
+    if out_dtype not in _OUT_CODES:
+        raise ValueError(f"output dtype must be torch.bfloat16 or torch.float32, got {out_dtype}")
+    for name, t in (("x", x), ("B", B), ("Bs", Bs)):
+        if t.dim() != 2:
+            raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+        if t.device != x.device:
+            raise ValueError("all tensors must be on the same device")
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"x must be torch.bfloat16, got {x.dtype}")
+    if B.dtype != FP8 or Bs.dtype != torch.float32:
+        raise ValueError(f"B must be torch.float8_e4m3fn and Bs torch.float32, got {B.dtype} and {Bs.dtype}")
+    M, K = x.shape
+    N, Kb = B.shape
+    if K != Kb:
+        raise ValueError(f"x is [M={M}, K={K}] but B is [N={N}, K={Kb}]")
+    if K % 128 != 0:
+        raise ValueError(f"K = {K} must be a multiple of 128 for the fused quantise-and-multiply call")
+    kblocks, nblocks = K // 128, -(-N // 128)
+    if tuple(Bs.shape) != (nblocks, kblocks):
+        raise ValueError(f"Bs must be [ceil(N/128), K/128] = [{nblocks}, {kblocks}], got {tuple(Bs.shape)}")
+    _require_cuda(x, "x")
+    dev = x.device
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or out.device != dev or (N > 1 and out.stride(1) != 1):
+        raise ValueError("out has the wrong shape, dtype, device or stride")
+    if M == 0 or N == 0:
+        return out
+    lib = _lib.load()
+    x_, B_, Bs_ = _row_major(x, 8), _row_major(B, 16), _row_major(Bs, 1)
+    v = resolve_variant(variant)
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200fp8_linear_workspace_bytes(M, N, K, v))
+        if ws_bytes < 0:
+            _lib.check(-ws_bytes, "b200fp8_linear_workspace_bytes")
+        ws = _workspace(dev, ws_bytes) if ws_bytes > 0 else None
+        st = lib.b200fp8_linear(
+            x_.data_ptr(), B_.data_ptr(), Bs_.data_ptr(), out.data_ptr(), M, N, K, _ld(x_), _ld(B_), _ld(Bs_), _ld(out),
+            _OUT_CODES[out_dtype], v, ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, status_word(dev).data_ptr(),
+            torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "b200fp8_linear")
+    return out
+
+
 def gemm_scatter(A, B, As, Bs, dst_ptrs, dst_lds, out_dtype: torch.dtype, variant=None) -> None:
     """C = A @ B.T written into several [M, >= N] buffers at once (b200fp8_gemm_scatter).
     dst_ptrs[0] / dst_lds[0] describe this GPU's own buffer, the others are device addresses of

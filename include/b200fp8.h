@@ -154,6 +154,26 @@ int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const fl
                          uint32_t* status_word, void* stream);
 
 /*
+ * Quantise-then-multiply in one call: C = e4m3_quant(x) . B^T with the activations given as
+ * bf16 [M, K] (row pitch ldx elements). The caller of the reference quantises its activations
+ * before the op (scripts/rebench_llm.py:130-133 builds A and As first); here the first launch
+ * quantises x with the arithmetic of b200fp8_quant_act and leaves the e4m3 rows and the
+ * K-block-major scales directly in the layout the GEMM kernel reads (inside `workspace`), the
+ * GEMM follows with programmatic dependent launch. Two launches instead of three, no
+ * separate q / scale tensors, and the result is bit-identical to b200fp8_quant_act followed
+ * by b200fp8_gemm. K must be a multiple of 128, x 16-byte aligned, ldx a multiple of 8; only
+ * the tile variants (or AUTO). Workspace: b200fp8_linear_workspace_bytes(M, N, K, variant)
+ * bytes (about M*K + 4*M*K/128), 256-byte aligned.
+ */
+int b200fp8_linear(const void* x_bf16, const void* B, const float* Bs, void* C,
+                   int64_t M, int64_t N, int64_t K,
+                   int64_t ldx, int64_t ldb, int64_t ld_bs, int64_t ldc,
+                   int out_dtype, int variant,
+                   void* workspace, size_t workspace_bytes,
+                   uint32_t* status_word, void* stream);
+int64_t b200fp8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
+
+/*
  * b200fp8_gemm whose result goes to a multimem (NVLink multicast) address: C_multimem is the
  * multicast view of one buffer that exists on every GPU of a multicast group (cuMulticast* /
  * torch symmetric memory rendezvous), offset to the first element of THIS call's column

@@ -248,3 +248,38 @@ def test_torch_compile_traces_the_op(device):
 
     eager = pkg.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.bfloat16) * 2
     assert torch.equal(f(A, B, As, Bs), eager)
+
+
+@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk"])
+@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (5, 256, 1024), (16, 1280, 2048), (130, 384, 256), (640, 4096, 1024)])
+def test_fused_quantise_and_multiply_equals_the_two_calls(device, M, N, K, variant):
+    """b200fp8_linear (activations quantised by the GEMM's own prep launch, straight into the
+    kernel's input layout) must give the bits of b200fp8_quant_act followed by b200fp8_gemm."""
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    x[0, :128] = 0                                     # an all-zero group: scale 0, zero bytes
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    Bq, Bs = oracle.quant_weight(w)
+    xd, Bd, Bsd = x.to(device), Bq.to(device), Bs.to(device)
+    for dtype in (torch.bfloat16, torch.float32):
+        fused = runtime.linear(xd, Bd, Bsd, dtype, variant=variant)
+        q, s = pkg.fp8_act_quant(xd)
+        two = runtime.gemm(q, Bd, s, Bsd, 128, 128, dtype, variant=variant)
+        assert torch.equal(fused, two)
+    runtime.check_device_status()
+    # and against the oracle end to end
+    qa, sa = oracle.quant_act(x)
+    ref = oracle.gemm_dequant(qa, Bq, sa, Bs)
+    assert oracle.bf16_ulp_error(runtime.linear(xd, Bd, Bsd, torch.bfloat16, variant=variant).cpu(), ref) <= 1
+
+
+def test_fp8_linear_public_wrapper(device):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 3, 512, generator=g).to(torch.bfloat16)
+    w = (torch.randn(256, 512, generator=g) * 0.02).to(torch.bfloat16)
+    Bq, Bs = oracle.quant_weight(w)
+    y = pkg.fp8_linear(x.to(device), Bq.to(device), Bs.to(device))
+    assert y.shape == (2, 3, 256) and y.dtype == torch.bfloat16
+    qa, sa = oracle.quant_act(x.reshape(-1, 512))
+    ref = oracle.gemm_dequant(qa, Bq, sa, Bs)
+    assert oracle.bf16_ulp_error(y.reshape(-1, 256).cpu(), ref) <= 1
