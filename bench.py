@@ -210,6 +210,14 @@ def extra_shapes(dev, peaks):
         out[f"decode_M{m}_N28672_K8192"] = {"ms": round(ms, 5), "gbs": round(gbs, 1),
                                             "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
         del a, b, sa, sb, c
+    # the same GEMM with one B scale per ROW of B (deep-gemm-helion's operand layout)
+    m, n, k = 4096, 4096, 8192
+    a, b, sa, _ = mk(m, n, k)
+    sb_row = torch.rand(n, k // 128, device=dev) * 0.5 + 0.5
+    ms = graph_ms(lambda: runtime.gemm_rowscale(a, b, sa, sb_row, 128, torch.bfloat16), 10)
+    tf = 2.0 * m * n * k / ms / 1e9
+    out["gemm_rowscale_4096x4096x8192"] = {"ms": round(ms, 5), "tflops": round(tf, 1), "frac_of_fp8_peak": round(tf / fp8_peak, 3)}
+    del a, b, sa, sb_row
     xs = [torch.randn(4096, 8192, device=dev).to(torch.bfloat16) for _ in range(3)]   # 3 x 64 MiB > L2
     i = [0]
 

@@ -25,7 +25,15 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
     """C = A @ B.T with block scales.  A: [M, K] float8_e4m3fn, B: [N, K] float8_e4m3fn,
     As: [M, K // bk] fp32, Bs: [N // bn, K // bk] fp32, block_size = [block_n, block_k]
     (only [128, 128]).  Returns [M, N] in output_dtype; fp32 accumulation.  bf16 and fp32
-    results are written by the kernel itself, other dtypes by a cast of the fp32 result."""
+    results are written by the kernel itself, other dtypes by a cast of the fp32 result.
+
+    The reference's own harness (finegrained-fp8-helion/bench.py:25-28) still calls this function
+    in an older form, `w8a8_block_fp8_matmul(A, B, sA, sB, 128)`: an int block size and one B scale
+    per ROW of B, sB [N, K // 128].  That form is accepted too and runs the row-scaled kernel."""
+    if isinstance(block_size, int):
+        res = runtime.gemm_rowscale(A, B, As, Bs, block_size,
+                                    output_dtype if output_dtype in _OUT_CODE else torch.float32)
+        return res if res.dtype == output_dtype else res.to(output_dtype)
     block_n, block_k = int(block_size[0]), int(block_size[1])
     code = _OUT_CODE.get(output_dtype)
     if code is None:

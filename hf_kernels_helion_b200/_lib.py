@@ -25,6 +25,10 @@ SIGNATURES = {
     "b200fp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                              c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p,
                              c_void_p]),
+    "b200fp8_gemm_rowscale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p,
+                                      c_void_p]),
+    "b200fp8_gemm_rowscale_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "b200fp8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200fp8_linear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),

@@ -65,6 +65,15 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256, false>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128, false>::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128>::THREADS,
+              128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false>), TileCfg<128>::THREADS,
+              128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128>::THREADS,
+              128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<128>), TileCfg<128>::THREADS,
+              128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_mc_kernel<256>), TileCfg<256>::THREADS,
@@ -276,6 +285,9 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   if (BN == 256 && args.sk_split >= 2) {
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, true>, ta, tb, args);
+  } else if (BN == 128 && args.BsT != nullptr) {
+    cfg.dynamicSmemBytes = TileCfg<128, false>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_rowb_kernel<128>, ta, tb, args);
   } else if (args.mc_store) {
     cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_mc_kernel<BN>, ta, tb, args);
@@ -419,7 +431,11 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
 struct FusedQuant {
   const void* x_bf16 = nullptr;
   int64_t ldx = 0;
+  // rowb: Bs is [N, ceil(K/128)], one scale per row of B (b200fp8_gemm_rowscale)
+  bool rowb = false;
 };
+
+int64_t bst_bytes(int64_t N, int64_t K) { return align_up(((K + 127) / 128) * align_up(N, 128) * 4, 256); }
 
 static int gemm_impl(bool mc, const void* A, const void* B, const float* As, const float* Bs, int n_dst, void* const* dst,
                      const int64_t* dst_ld, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as,
@@ -482,7 +498,9 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
+  if (fq.rowb) variant = B200FP8_VARIANT_TILE128;   // the row-scaled promotion exists for the 128-wide tile only
   const bool multi = n_dst > 1 || mc;
+  if (fq.rowb && (multi || fused_q)) return B200FP8_ERR_VARIANT;
   if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
   if (multi && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
 
@@ -496,7 +514,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
       variant == B200FP8_VARIANT_TILE256_SK) {
     const bool sk = variant == B200FP8_VARIANT_TILE256_SK;
     const int64_t prefix = fused_q ? linear_prefix_bytes(M, K) : tile_workspace_bytes(M, K);
-    const int64_t need = prefix + (sk ? skp.partial_bytes : 0);
+    const int64_t need = prefix + (sk ? skp.partial_bytes : 0) + (fq.rowb ? bst_bytes(N, K) : 0);
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_ERR_ALIGN;
     GemmArgs args;
@@ -526,6 +544,18 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
           static_cast<const uint8_t*>(A), a_pad, K, lda, align_up(K, 16));
       st = launch_status();
       if (st != B200FP8_OK) return st;
+    }
+    args.BsT = nullptr;
+    args.n_pad = align_up(N, 128);
+    if (fq.rowb) {
+      // second transposition: the row scales of B, K-block-major (same kernel, B in the role of A)
+      float* bst = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + prefix);
+      const dim3 grid(static_cast<unsigned>(args.n_pad / 32), static_cast<unsigned>((kblocks + 31) / 32));
+      tile_prep_kernel<<<grid, 256, 0, stream>>>(Bs, bst, N, args.n_pad, static_cast<int>(kblocks), ld_bs, nullptr,
+                                                 nullptr, K, 0, 0);
+      st = launch_status();
+      if (st != B200FP8_OK) return st;
+      args.BsT = bst;
     }
     args.As = As;
     args.Bs = Bs;
@@ -605,6 +635,24 @@ int b200fp8_gemm(const void* A, const void* B, const float* As, const float* Bs,
   const int64_t ld[1] = {ldc};
   return gemm_impl(false, A, B, As, Bs, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype, variant, workspace,
                    workspace_bytes, status_word, stream);
+}
+
+int b200fp8_gemm_rowscale(const void* A, const void* B, const float* As, const float* Bs_row, void* C, int64_t M,
+                          int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc,
+                          int out_dtype, void* workspace, size_t workspace_bytes, uint32_t* status_word,
+                          void* stream) {
+  void* dst[1] = {C};
+  const int64_t ld[1] = {ldc};
+  FusedQuant fq;
+  fq.rowb = true;
+  return gemm_impl(false, A, B, As, Bs_row, 1, dst, ld, M, N, K, lda, ldb, ld_as, ld_bs, out_dtype,
+                   B200FP8_VARIANT_TILE128, workspace, workspace_bytes, status_word, stream, fq);
+}
+
+int64_t b200fp8_gemm_rowscale_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
+  if (M == 0 || N == 0 || K == 0) return 0;
+  return tile_workspace_bytes(M, K) + bst_bytes(N, K);
 }
 
 int b200fp8_linear(const void* x_bf16, const void* B, const float* Bs, void* C, int64_t M, int64_t N, int64_t K,

@@ -70,6 +70,11 @@ struct GemmArgs {
   int64_t dst_ld[8];
   const float* AsT;   // [ceil(K/128)][m_pad] token scales, K-block-major (written by tile_prep_kernel)
   int64_t m_pad;      // M rounded up to 128
+  // Row-scaled B (kernels instantiated with ROWB = true): one scale per row of B and K block,
+  // given as Bs [N, ceil(K/128)] and re-laid K-block-major by tile_prep_kernel as BsT[kb][n_pad]
+  // (n_pad = N rounded up to 128, padding zero); Bs / ld_bs are then unused by the GEMM kernel.
+  const float* BsT;
+  int64_t n_pad;
   const float* As;
   const float* Bs;
   void* C;
@@ -219,7 +224,9 @@ struct DstMaps {
 
 // MULTI: the result leaves through the shared-memory staging area; MC (with MULTI): by
 // multimem.st to a multicast address, otherwise by TMA stores to up to eight destinations.
-template <int BN, bool MULTI, bool SK, bool MC = false>
+// ROWB: B carries one scale per ROW and K block (the deep-gemm layout) instead of one per
+// 128 x 128 block: the promotion multiplies every accumulator column by its own scale.
+template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmArgs& args, const CUtensorMap* dmaps) {
   using Cfg = TileCfg<BN, MULTI>;
@@ -401,6 +408,46 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[g][j] = make_float2(0.f, 0.f);
 
+      // Row-scaled B, BN = 128: this thread's 64 columns have 64 different B scales per K
+      // block, the same for all lanes of the warp. They are fetched (16 broadcast loads of 16
+      // bytes from the K-block-major copy) before the wait for the MMA, so that they arrive
+      // while the warp waits; then acc += p * (sa * sb[col]) costs a multiply and an FMA.
+      auto promote_rowb = [&](float sa, const float* sbt) -> bool {
+        static_assert(!ROWB || CHUNKS == 2, "row-scaled B is built for the 128-wide tile only");
+        float4 sv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sv[i] = __ldg(reinterpret_cast<const float4*>(sbt) + i);
+        const uint32_t ts = it % TS;
+        const uint32_t tph = (it / TS) & 1u;
+        ++it;
+        if (!__all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word))) return false;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + lane_col + ts * BN;
+        uint32_t pa[32], pb[32];
+        tmem_ld_32x32(taddr, pa);
+        tmem_ld_32x32(taddr + 32, pb);
+        tmem_ld_wait_32(pa);
+        tmem_ld_wait_32(pb);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[ts]);
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int c = 32 * g + 2 * j;
+            const float4 s4 = sv[c >> 2];
+            const float s_lo = (c & 2) ? s4.z : s4.x;
+            const float s_hi = (c & 2) ? s4.w : s4.y;
+            const float p_lo = __uint_as_float(g ? pb[2 * j] : pa[2 * j]);
+            const float p_hi = __uint_as_float(g ? pb[2 * j + 1] : pa[2 * j + 1]);
+            acc[g & (CHUNKS - 1)][j].x = fmaf(p_lo, sa * s_lo, acc[g & (CHUNKS - 1)][j].x);
+            acc[g & (CHUNKS - 1)][j].y = fmaf(p_hi, sa * s_hi, acc[g & (CHUNKS - 1)][j].y);
+          }
+        }
+        return true;
+      };
+
       // One K block: wait for its partial in TMEM, pull it into registers in 32-column
       // chunks with two tcgen05.ld in flight, hand the TMEM stage back as soon as the last
       // chunk has landed (before its FMAs).
@@ -453,7 +500,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       for (int j = 0; j < PF; ++j) {
         const int k = seg.kb_begin + j < seg.kb_end ? seg.kb_begin + j : kb_last;
         sa_c[j] = __ldg(as_col + k * args.m_pad);
-        sb_c[j] = __ldg(bs_row + k);
+        sb_c[j] = ROWB ? 1.f : __ldg(bs_row + k);
       }
       for (int kb0 = seg.kb_begin; ok && kb0 < seg.kb_end; kb0 += PF) {
 #pragma unroll
@@ -461,12 +508,16 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
           int k = kb0 + PF + j;
           k = k < seg.kb_end ? k : kb_last;
           sa_n[j] = __ldg(as_col + k * args.m_pad);
-          sb_n[j] = __ldg(bs_row + k);
+          sb_n[j] = ROWB ? 1.f : __ldg(bs_row + k);
         }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
           if (ok && kb0 + j < seg.kb_end) {
-            ok = promote(sa_c[j] * sb_c[j]);
+            if constexpr (ROWB) {
+              ok = promote_rowb(sa_c[j], args.BsT + static_cast<int64_t>(kb0 + j) * args.n_pad + col0);
+            } else {
+              ok = promote(sa_c[j] * sb_c[j]);
+            }
           }
         }
 #pragma unroll
@@ -666,6 +717,14 @@ __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
   gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
+}
+
+// Row-scaled B (deep-gemm layout): single destination, 128-wide tiles.
+template <int BN>
+__global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
+gemm_tile_rowb_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmArgs args) {
+  gemm_tile_body<BN, false, false, false, true>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Multicast form: args.dst[0] is a multimem address; every 128-byte row segment of a finished

@@ -135,6 +135,51 @@ def gemm(A, B, As, Bs, block_n: int, block_k: int, out_dtype: torch.dtype, varia
     return out
 
 
+def gemm_rowscale(A, B, As, Bs, block_k: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """C = A @ B.T with As [M, ceil(K/128)] and one B scale per ROW of B, Bs [N, ceil(K/128)]
+    (b200fp8_gemm_rowscale; the operand layout of deep-gemm-helion's gemm_fp8_fp8_bf16_nt)."""
+    if int(block_k) != 128:
+        raise ValueError(f"block_size must be 128, got {block_k}")
+    if out_dtype not in _OUT_CODES:
+        raise ValueError(f"output dtype must be torch.bfloat16 or torch.float32, got {out_dtype}")
+    for name, t in (("A", A), ("B", B), ("As", As), ("Bs", Bs)):
+        if t.dim() != 2:
+            raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+        if t.device != A.device:
+            raise ValueError("all tensors must be on the same device")
+    if A.dtype != FP8 or B.dtype != FP8:
+        raise ValueError(f"A and B must be torch.float8_e4m3fn, got {A.dtype} and {B.dtype}")
+    if As.dtype != torch.float32 or Bs.dtype != torch.float32:
+        raise ValueError(f"As and Bs must be torch.float32, got {As.dtype} and {Bs.dtype}")
+    M, K = A.shape
+    N, Kb = B.shape
+    if K != Kb:
+        raise ValueError(f"A is [M={M}, K={K}] but B is [N={N}, K={Kb}]")
+    kblocks = -(-K // 128)
+    if tuple(As.shape) != (M, kblocks) or tuple(Bs.shape) != (N, kblocks):
+        raise ValueError(f"As must be [{M}, {kblocks}] and Bs [{N}, {kblocks}], got {tuple(As.shape)} and {tuple(Bs.shape)}")
+    _require_cuda(A, "A")
+    dev = A.device
+    out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    if M == 0 or N == 0:
+        return out
+    lib = _lib.load()
+    A_, B_ = _row_major(A, 16), _row_major(B, 16)
+    As_, Bs_ = _row_major(As, 1), _row_major(Bs, 1)
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200fp8_gemm_rowscale_workspace_bytes(M, N, K))
+        if ws_bytes < 0:
+            _lib.check(-ws_bytes, "b200fp8_gemm_rowscale_workspace_bytes")
+        ws = _workspace(dev, ws_bytes) if ws_bytes > 0 else None
+        st = lib.b200fp8_gemm_rowscale(
+            A_.data_ptr(), B_.data_ptr(), As_.data_ptr(), Bs_.data_ptr(), out.data_ptr(),
+            M, N, K, _ld(A_), _ld(B_), _ld(As_), _ld(Bs_), _ld(out), _OUT_CODES[out_dtype],
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(st, "b200fp8_gemm_rowscale")
+    return out
+
+
 def linear(x, B, Bs, out_dtype: torch.dtype, variant=None, out=None) -> torch.Tensor:
     """C = quantise(x) @ B.T in one library call (b200fp8_linear): x is bf16 [M, K] with K a
     multiple of 128; the first launch quantises it per 1x128 group straight into the layout the

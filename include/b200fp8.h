@@ -154,6 +154,25 @@ int b200fp8_gemm_scatter(const void* A, const void* B, const float* As, const fl
                          uint32_t* status_word, void* stream);
 
 /*
+ * The same GEMM with one B scale per ROW of B and K block: Bs_row is [N, ceil(K/128)] fp32
+ * (row pitch ld_bs), everything else as b200fp8_gemm. This is the operand layout of the
+ * reference's second block-FP8 kernel, deep-gemm-helion
+ * (deep-gemm-helion/deep-gemm-helion/torch-ext/deep_gemm_helion/fp8.py:13-29:
+ * acc += dot(a, b^T) * sA[m, kb][:, None] * sB[n, kb][None, :], bf16 result;
+ * torch-ext/deep_gemm_helion/op.py:7-10). Runs on the 128 x 128 tile kernel; the promotion
+ * multiplies every accumulator column by its own scale (one multiply more per element than
+ * the block-scaled form). Workspace: b200fp8_gemm_rowscale_workspace_bytes(M, N, K) bytes,
+ * 256-byte aligned (both scale sets re-laid K-block-major).
+ */
+int b200fp8_gemm_rowscale(const void* A, const void* B, const float* As, const float* Bs_row, void* C,
+                          int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs, int64_t ldc,
+                          int out_dtype,
+                          void* workspace, size_t workspace_bytes,
+                          uint32_t* status_word, void* stream);
+int64_t b200fp8_gemm_rowscale_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
  * Quantise-then-multiply in one call: C = e4m3_quant(x) . B^T with the activations given as
  * bf16 [M, K] (row pitch ldx elements). The caller of the reference quantises its activations
  * before the op (scripts/rebench_llm.py:130-133 builds A and As first); here the first launch

@@ -178,6 +178,50 @@ def gemm_dequant(A, B, As, Bs, block_n: int = 128, block_k: int = 128) -> torch.
     return (A.to(torch.float32) * saf) @ (B.to(torch.float32) * sbf).T
 
 
+def gemm_rowscale_blockwise(A, B, As, Bs_row, block_k: int = 128, tile: int = 128) -> torch.Tensor:
+    """fp32 [M, N] with one B scale per ROW of B: the loop of deep-gemm-helion's kernel
+    (deep-gemm-helion/deep-gemm-helion/torch-ext/deep_gemm_helion/fp8.py:19-28):
+    acc += dot(a, b^T) * sA[tm, kb][:, None] * sB[tn, kb][None, :] per K block, multiplication
+    order as written there. The kernel stores bf16 (fp8.py:29); the cast is left to the caller."""
+    M, K = A.shape
+    N = B.shape[0]
+    Af = A.to(torch.float32)
+    Bf = B.to(torch.float32)
+    out = torch.empty(M, N, dtype=torch.float32)
+    for m0 in range(0, M, tile):
+        m1 = min(m0 + tile, M)
+        for n0 in range(0, N, tile):
+            n1 = min(n0 + tile, N)
+            acc = torch.zeros(m1 - m0, n1 - n0, dtype=torch.float32)
+            for k0 in range(0, K, block_k):
+                k1 = min(k0 + block_k, K)
+                kb = k0 // block_k
+                acc = acc + (Af[m0:m1, k0:k1] @ Bf[n0:n1, k0:k1].T) * As[m0:m1, kb][:, None] * Bs_row[n0:n1, kb][None, :]
+            out[m0:m1, n0:n1] = acc
+    return out
+
+
+def gemm_rowscale_dequant(A, B, As, Bs_row, block_k: int = 128) -> torch.Tensor:
+    """fp32 [M, N]; dequantise with per-row scales on both sides, then one fp32 matmul
+    (deep-gemm-helion/bench.py:11-14 `ref`, before its bf16 cast)."""
+    K = A.shape[1]
+    saf = As.repeat_interleave(block_k, dim=1)[:, :K]
+    sbf = Bs_row.repeat_interleave(block_k, dim=1)[:, :K]
+    return (A.to(torch.float32) * saf) @ (B.to(torch.float32) * sbf).T
+
+
+def make_rowscale_inputs(M: int, N: int, K: int, seed: int = 0):
+    """Operands with the distribution of deep-gemm-helion/bench.py:24-27: e4m3(randn * 0.3),
+    scales U[0.5, 1), one per row and K block on both sides; generated on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    kb = _ceil_div(K, GROUP)
+    A = (torch.randn(M, K, generator=g) * 0.3).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.3).to(torch.float8_e4m3fn)
+    As = torch.rand(M, kb, generator=g) * 0.5 + 0.5
+    Bs = torch.rand(N, kb, generator=g) * 0.5 + 0.5
+    return A, B, As, Bs
+
+
 def w8a8_block_fp8_matmul(A, B, As, Bs, block_size, output_dtype=torch.float32) -> torch.Tensor:
     block_n, block_k = int(block_size[0]), int(block_size[1])
     return gemm_blockwise(A, B, As, Bs, block_n, block_k).to(output_dtype)

@@ -23,6 +23,11 @@ Two pieces of reference code are executed, unmodified, on the CPU:
    (``block_size=[None, block_n]``), is taken from the shipped sm_100 heuristic
    ``_helion_aot_fp8_cuda_sm100.py``.
 
+3. ``deep-gemm-helion/deep-gemm-helion/torch-ext/deep_gemm_helion/fp8.py`` (the second
+   block-FP8 kernel, one B scale per row of B; lines 13-29) under the same stand-in, and
+   ``deep-gemm-helion/bench.py`` function ``ref`` (lines 11-14) taken out with ``ast``;
+   ``python tests/golden/make_golden.py deep-gemm`` writes only these fixtures.
+
 The inputs are the seeded synthetic tensors of oracle/fp8_oracle.py; each fixture
 stores the inputs' bytes (small cases) or their SHA-256 (the 512x512x2048
 configuration) next to the outputs so a drift of the generator is told apart from a
@@ -112,7 +117,7 @@ def _make_helion_stub(m_tile_for):
 
     def tile(sizes, block_size=None):
         if isinstance(sizes, (list, tuple)):
-            bs = list(block_size)
+            bs = [None] * len(sizes) if block_size is None else list(block_size)
             bs = [state["m_tile"] if b is None else int(b) for b in bs]
             M, N = int(sizes[0]), int(sizes[1])
             for m0 in range(0, M, bs[0]):
@@ -145,7 +150,7 @@ def _make_helion_stub(m_tile_for):
         return deco
 
     hl.tile, hl.zeros, hl.dot, hl.constexpr = tile, zeros, dot, int
-    helion.aot_kernel, helion.language = aot_kernel, hl
+    helion.aot_kernel, helion.kernel, helion.language = aot_kernel, aot_kernel, hl
     return helion, hl
 
 
@@ -166,6 +171,49 @@ def load_reference_kernel():
     finally:
         del sys.modules["helion"], sys.modules["helion.language"]
     return mod._w8a8_block_fp8_matmul
+
+
+# --------------------------------------------------------------------------- (3) deep-gemm-helion
+
+DG_DIR = REF / "deep-gemm-helion" / "deep-gemm-helion" / "torch-ext" / "deep_gemm_helion"
+
+
+def load_deep_gemm_kernel():
+    """deep_gemm_helion/fp8.py:13-29 under the same eager stand-in. Its tiles over [M, N] are left
+    entirely to the autotuner (`hl.tile([M, N])`); 128 x 128 is used."""
+    helion, hl = _make_helion_stub(lambda *args: 128)
+    sys.modules["helion"], sys.modules["helion.language"] = helion, hl
+    try:
+        spec = importlib.util.spec_from_file_location("_ref_dg_fp8", DG_DIR / "fp8.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        del sys.modules["helion"], sys.modules["helion.language"]
+    return mod._fp8_blockwise_gemm
+
+
+def load_deep_gemm_bench_ref():
+    src = (REF / "deep-gemm-helion" / "bench.py").read_text()
+    tree = ast.parse(src)
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "ref")
+    ns = {"torch": torch}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), "reference:deep-gemm-helion/bench.py", "exec"), ns)
+    return ns["ref"]
+
+
+def make_deep_gemm_fixtures():
+    kernel, bench_ref = load_deep_gemm_kernel(), load_deep_gemm_bench_ref()
+    for name, (M, N, K, seed) in {"rowscale_96x256x384": (96, 256, 384, 11), "rowscale_130x128x256": (130, 128, 256, 12),
+                                  "rowscale_1x384x512": (1, 384, 512, 13)}.items():
+        A, B, As, Bs = oracle.make_rowscale_inputs(M, N, K, seed)
+        out_kernel = kernel(A, B, As, Bs, 128)              # bf16, as the op returns it
+        out_bench = bench_ref(A, B, As, Bs, 128)            # bf16
+        np.savez_compressed(HERE / f"{name}.npz", M=M, N=N, K=K, seed=seed,
+                            A=A.view(torch.uint8).numpy(), B=B.view(torch.uint8).numpy(),
+                            As=As.numpy(), Bs=Bs.numpy(),
+                            out_kernel_bf16_bits=out_kernel.view(torch.int16).numpy(),
+                            out_bench_bf16_bits=out_bench.view(torch.int16).numpy())
+        print(name, "kernel-vs-bench max/rms", oracle.max_err_over_rms(out_kernel.float(), out_bench.float()))
 
 
 # --------------------------------------------------------------------------- fixtures
@@ -207,4 +255,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["deep-gemm"]:
+        make_deep_gemm_fixtures()
+    else:
+        main()
+        make_deep_gemm_fixtures()

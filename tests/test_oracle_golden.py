@@ -149,3 +149,25 @@ def test_quant_weight_blocks():
             assert s[nb, kb] == blk.abs().max() / 448
             assert torch.equal((blk / s[nb, kb]).to(torch.float8_e4m3fn).view(torch.uint8),
                                q[nb * 128:(nb + 1) * 128, kb * 128:(kb + 1) * 128].view(torch.uint8))
+
+
+ROWSCALE = ["rowscale_96x256x384", "rowscale_130x128x256", "rowscale_1x384x512"]
+
+
+@pytest.mark.parametrize("name", ROWSCALE)
+def test_rowscale_oracles_match_reference_deep_gemm_source(name):
+    """Row-scaled B (deep-gemm-helion): the blockwise restatement against the reference kernel's
+    own output, the dequantise-then-matmul one against the reference harness's `ref`; both
+    fixtures were produced by running the reference's source files (tests/golden/make_golden.py)."""
+    g = np.load(GOLDEN / f"{name}.npz")
+    A = torch.from_numpy(g["A"]).view(torch.float8_e4m3fn)
+    B = torch.from_numpy(g["B"]).view(torch.float8_e4m3fn)
+    As, Bs = torch.from_numpy(g["As"]), torch.from_numpy(g["Bs"])
+    M, N, K, seed = int(g["M"]), int(g["N"]), int(g["K"]), int(g["seed"])
+    A2, B2, As2, Bs2 = oracle.make_rowscale_inputs(M, N, K, seed)
+    assert torch.equal(A.view(torch.uint8), A2.view(torch.uint8)) and torch.equal(B.view(torch.uint8), B2.view(torch.uint8))
+    assert torch.equal(As, As2) and torch.equal(Bs, Bs2) and tuple(Bs.shape) == (N, K // 128)
+    want_kernel = torch.from_numpy(g["out_kernel_bf16_bits"]).view(torch.bfloat16)
+    want_bench = torch.from_numpy(g["out_bench_bf16_bits"]).view(torch.bfloat16)
+    assert torch.equal(oracle.gemm_rowscale_blockwise(A, B, As, Bs).to(torch.bfloat16), want_kernel)
+    assert torch.equal(oracle.gemm_rowscale_dequant(A, B, As, Bs).to(torch.bfloat16), want_bench)
