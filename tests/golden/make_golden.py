@@ -1,7 +1,7 @@
 """Generate tests/golden/*.npz from the REFERENCE's own source files.
 
 Run once, in a container that has the reference checkout (default
-``/root/reference``, override with ``REFERENCE_ROOT``):
+``~/reference``, override with ``REFERENCE_ROOT``):
 
     python tests/golden/make_golden.py
 
@@ -50,7 +50,7 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
 from oracle import fp8_oracle as oracle  # noqa: E402
 
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("REFERENCE_ROOT", str(Path.home() / "reference")))
 FP8_DIR = REF / "finegrained-fp8-helion" / "finegrained-fp8-helion" / "torch-ext" / "finegrained_fp8_helion"
 
 
