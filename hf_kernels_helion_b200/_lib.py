@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200fp8_gemm_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t,
                                      c_void_p, c_void_p]),
+    "b200fp8_peer_barrier": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p, c_void_p]),
     "b200fp8_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "b200fp8_ipc_open": (c_int, [c_void_p, c_void_p]),
     "b200fp8_ipc_close": (c_int, [c_void_p]),

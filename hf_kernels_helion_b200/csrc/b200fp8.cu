@@ -744,6 +744,19 @@ int b200fp8_ipc_close(void* base) {
   return B200FP8_OK;
 }
 
+int b200fp8_peer_barrier(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch, uint32_t* status_word,
+                         void* stream) {
+  if (flag_arrays == nullptr) return B200FP8_ERR_NULL;
+  if (n < 1 || n > 8 || rank < 0 || rank >= n) return B200FP8_ERR_SHAPE;
+  PeerFlags f;
+  for (int i = 0; i < 8; ++i) {
+    f.p[i] = i < n ? flag_arrays[i] : nullptr;
+    if (i < n && (f.p[i] == nullptr || (reinterpret_cast<uintptr_t>(f.p[i]) & 3u) != 0)) return B200FP8_ERR_NULL;
+  }
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, epoch, status_word);
+  return launch_status();
+}
+
 int b200fp8_gemm_decode_static(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M,
                                int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ld_as, int64_t ld_bs,
                                int64_t ldc, int out_dtype, uint32_t* status_word, void* stream_) {

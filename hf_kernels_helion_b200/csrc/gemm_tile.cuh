@@ -805,6 +805,36 @@ tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int6
   }
 }
 
+// Barrier between the GPUs of a node after a multi-destination GEMM: one warp per GPU. Lane p
+// (p < n) stores `epoch` into slot `rank` of GPU p's flag array (a release store at system scope
+// over NVLink), then polls slot p of its own array until GPU p's store of the same epoch has
+// arrived. Epochs only grow, so a late reader never misses one (comparison is wrap-safe).
+// The wait is bounded (~10 s of SM clocks, generous because the ranks' hosts may be seconds
+// apart at start-up); on expiry the status word gets B200FP8_DEV_WAIT_TIMEOUT and the kernel
+// returns. The kernels of different GPUs wait on one another: never run two ranks on one GPU.
+struct PeerFlags {
+  uint32_t* p[8];
+};
+
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(PeerFlags flags, int n, int rank, uint32_t epoch, uint32_t* status_word) {
+  const int lane = threadIdx.x;
+  if (lane >= n) return;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[lane] + rank), "r"(epoch) : "memory");
+  const uint32_t* mine = flags.p[rank] + lane;
+  const long long t0 = clock64();
+  constexpr long long kLimit = 20000000000ll;
+  for (uint32_t polls = 0;; ++polls) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(v - epoch) >= 0) break;
+    if ((polls & 255u) == 255u && clock64() - t0 > kLimit) {
+      if (status_word != nullptr) atomicOr(status_word, B200FP8_DEV_WAIT_TIMEOUT);
+      break;
+    }
+  }
+}
+
 // Launch-side preparation of one GEMM call, grid = (m_pad / 32, ceil(num_kb / 32), 1 or 2):
 //   z = 0  AsT[kb][m] = As[m][kb] for m < M, 0 for M <= m < m_pad: 32 x 32 tiles through
 //          shared memory so that both the row-major reads and the K-block-major writes are

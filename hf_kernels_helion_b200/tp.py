@@ -45,7 +45,15 @@ class PeerBuffers:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.local = torch.empty((M, N), dtype=dtype, device=device)
+        # one allocation: the [M, N] buffer followed by a 256-byte tail that holds this rank's eight
+        # barrier flags (zero at start), so that one IPC mapping gives the peers both
+        esize = torch.empty((), dtype=dtype).element_size()
+        self._body = -(-(M * N * esize) // 256) * 256
+        raw = torch.empty(self._body + 256, dtype=torch.uint8, device=device)
+        raw[self._body:].zero_()
+        self.local = raw[:M * N * esize].view(dtype).view(M, N)
+        self.flags = raw[self._body:self._body + 32].view(torch.int32)
+        self._raw = raw
         lib = _lib.load()
         handle = ctypes.create_string_buffer(64)
         offset = ctypes.c_int64(0)
@@ -67,6 +75,25 @@ class PeerBuffers:
 
     def ptr(self, r: int) -> int:
         return self._ptrs[r]
+
+    def flag_ptr(self, r: int) -> int:
+        """Device address, valid in this process, of rank r's barrier flag array."""
+        return self._ptrs[r] + self._body
+
+    def barrier(self, epoch: int) -> None:
+        """Enqueue the device-side barrier (b200fp8_peer_barrier) on the current stream: work queued
+        behind it sees what every rank's kernels queued before their barrier of the same epoch wrote."""
+        import ctypes
+
+        from . import _lib, runtime
+
+        dev = self.local.device
+        arr = (ctypes.c_void_p * self.world)(*[self.flag_ptr(r) for r in range(self.world)])
+        with torch.cuda.device(dev):
+            st = _lib.load().b200fp8_peer_barrier(arr, self.world, self.rank, epoch & 0xFFFFFFFF,
+                                                  runtime.status_word(dev).data_ptr(),
+                                                  torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(st, "b200fp8_peer_barrier")
 
     def close(self) -> None:
         from . import _lib
@@ -136,6 +163,9 @@ class ShardedFp8Linear:
             raise ValueError("the local weight slice must be a whole number of 128-row blocks")
         self._injected = matmul is not None
         self.matmul = matmul
+        # forward_fused: True = the ranks meet in a one-warp kernel that exchanges flags over NVLink
+        # (b200fp8_peer_barrier); False = a one-element NCCL all-reduce plays the barrier
+        self.device_barrier = True
         self._gather_buf = None
 
     @classmethod
@@ -181,8 +211,9 @@ class ShardedFp8Linear:
     def forward_fused(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
         """Contiguous C [M, N] on every rank with the exchange fused into the GEMM: the kernel's
         epilogue stores this rank's column slice into the [M, N] buffer of EVERY rank (peer
-        stores over NVLink), and one tiny all-reduce afterwards is the barrier that tells each
-        rank that all slices have arrived.  No all-gather, no transpose copy.
+        stores over NVLink), and a one-warp flag-exchange kernel afterwards (or, with
+        device_barrier = False, one tiny all-reduce) is the barrier that tells each rank that all
+        slices have arrived.  No all-gather, no transpose copy, no NCCL call on the data path.
 
         Two buffer sets alternate between calls: the result returned by call i stays valid until
         call i + 2 is issued, and work that reads it must be enqueued on the current stream
@@ -197,6 +228,7 @@ class ShardedFp8Linear:
             self._peer = [PeerBuffers(M, self.N, output_dtype, A.device, self.group) for _ in range(2)]
             self._peer_key = key
             self._peer_turn = 0
+            self._epoch = 0
             self._flag = torch.zeros(1, dtype=torch.float32, device=A.device)
         pb = self._peer[self._peer_turn]
         self._peer_turn ^= 1
@@ -207,7 +239,11 @@ class ShardedFp8Linear:
         ptrs = [pb.ptr(r) + col_bytes for r in order]
         runtime.gemm_scatter(A, self.B, As, self.Bs, ptrs, [self.N] * self.world, output_dtype)
         if self.world > 1:
-            dist.all_reduce(self._flag, group=self.group)
+            if self.device_barrier:
+                self._epoch += 1
+                self._peer[0].barrier(self._epoch)      # one flag set serves both buffer sets
+            else:
+                dist.all_reduce(self._flag, group=self.group)
         return pb.local
 
     def forward_multimem(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:

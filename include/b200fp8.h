@@ -211,6 +211,20 @@ int b200fp8_gemm_multicast(const void* A, const void* B, const float* As, const 
                            uint32_t* status_word, void* stream);
 
 /*
+ * Barrier between the n (<= 8) GPUs of a node that follow a b200fp8_gemm_scatter with one another's
+ * reads: flag_arrays[p] is GPU p's array of n 32-bit flags (zero at start; the caller's own
+ * for p == rank, the others mapped with b200fp8_ipc_open), epoch a number that grows by one
+ * per barrier, the same on every GPU. The kernel (one warp, enqueued on `stream` behind the GEMM)
+ * publishes `epoch` to every GPU and waits until every GPU has published it; work enqueued
+ * behind it may read the buffers the peers wrote. The wait is bounded (about 10 s); on expiry
+ * B200FP8_DEV_WAIT_TIMEOUT is set in the status word. Each GPU of the group must run its own
+ * process's call on its own device: the kernels wait for one another. No counterpart in the
+ * reference.
+ */
+int b200fp8_peer_barrier(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch,
+                         uint32_t* status_word, void* stream);
+
+/*
  * CUDA IPC helpers for b200fp8_gemm_scatter (no counterpart in the reference). export: a
  * 64-byte handle of the device allocation that contains ptr, and ptr's byte offset inside it;
  * the handle travels to the other process by any host channel. open: maps that allocation

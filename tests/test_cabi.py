@@ -69,6 +69,27 @@ def test_argument_errors_need_no_device(lib):
     assert lib.b200fp8_gemm(p16, p16, p16, p16, p16, 4, 4, 128, 128, 128, 1, 1, 2, 0, 0, null, 0, null, null) == 2
 
 
+def test_argument_errors_of_the_newer_entry_points(lib):
+    null = None
+    buf = ctypes.create_string_buffer(4096)
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+    # fused quantise-and-multiply: K must be a multiple of 128, x must be there
+    assert lib.b200fp8_linear(null, p16, p16, p16, 4, 128, 128, 128, 128, 1, 128, 0, 0, null, 0, null, null) == 1
+    assert lib.b200fp8_linear_workspace_bytes(-1, 1, 1, 0) == -2
+    assert lib.b200fp8_linear_workspace_bytes(16, 28672, 8192, 3) == -5            # no stream-K form of it
+    assert lib.b200fp8_linear_workspace_bytes(16, 28672, 8192, 2) == 64 * 128 * 4 + 16 * 8192
+    # row-scaled B: same checks as the block-scaled GEMM
+    assert lib.b200fp8_gemm_rowscale(null, null, null, null, null, -1, 1, 1, 1, 1, 1, 1, 1, 0, null, 0, null, null) == 2
+    assert lib.b200fp8_gemm_rowscale(null, null, null, null, null, 1, 1, 1, 1, 1, 1, 1, 1, 7, null, 0, null, null) == 4
+    assert lib.b200fp8_gemm_rowscale_workspace_bytes(256, 512, 1024) == 8 * 256 * 4 + 8 * 512 * 4
+    # peer barrier: group size and rank are checked before anything is launched
+    arr = (ctypes.c_void_p * 8)(*([p16] * 8))
+    assert lib.b200fp8_peer_barrier(null, 2, 0, 1, null, null) == 1
+    assert lib.b200fp8_peer_barrier(arr, 0, 0, 1, null, null) == 2
+    assert lib.b200fp8_peer_barrier(arr, 9, 0, 1, null, null) == 2
+    assert lib.b200fp8_peer_barrier(arr, 2, 2, 1, null, null) == 2
+
+
 def test_workspace_and_variant_queries(lib):
     AUTO, T128, T256, SK = 0, 1, 2, 3
     ast = 64 * 4096 * 4                                       # K-block-major copy of As: [K/128][M] fp32
