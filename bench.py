@@ -444,7 +444,9 @@ def main_ours(args):
                             "since the N-sharded layout needs all of A on every GPU), the [M,N] bf16 result comes back to pinned host memory once per step "
                             "(each rank reads back its M/n_gpus row block of the assembled result); "
                             "read-back of step i overlaps upload + math of step i+1 (second stream); the quantised weight is a resident parameter"},
-            "gpu_launches": steps * 2,
+            # per step: quant_act_contig_kernel, tile_prep_kernel, the GEMM kernel; N > 1 adds the exchange's
+            # barrier kernel (fused) or NCCL's all-gather plus the slot -> [M,N] copy (not counted: not ours)
+            "gpu_launches": steps * (3 + (1 if world > 1 and args.exchange == "fused" else 0)),
             "roofline": {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp8_peak, "traffic": traffic,
                          "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of MEASURED_PEAKS.json ({peaks['source']}): "
