@@ -87,12 +87,18 @@ struct GemmArgs {
 #endif
 };
 
-template <int BN_, bool MULTI_ = false>
+// A_ROWS_: rows of A that the TMA actually brings in per K block (128; 16 or 64 for decode shapes
+// with M <= 16 / M <= 64). The MMA always reads 128 rows from the A slot; with a short slot
+// (2 or 8 KiB) the remaining rows alias the B tile that follows it in the same stage - garbage
+// that lands in accumulator rows which are never stored - and the bytes saved buy one or two
+// more pipeline stages (weight streaming is bound by the bytes in flight per SM).
+template <int BN_, bool MULTI_ = false, int A_ROWS_ = 128>
 struct TileCfg {
   static constexpr int BM = 128;
   static constexpr int BN = BN_;
   static constexpr int BK = 128;  // fp8 elements = bytes = one 128-byte swizzle span
-  static constexpr int STAGES = (BN_ == 128) ? 6 : 4;
+  static constexpr int A_ROWS = A_ROWS_;
+  static constexpr int STAGES = (A_ROWS_ == 16) ? 6 : (A_ROWS_ == 64) ? 5 : (BN_ == 128) ? 6 : 4;
   static constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quarter
   static constexpr int EPI_COLS = BN_ / 2;          // accumulator columns (registers) per epilogue thread
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
@@ -114,7 +120,10 @@ struct TileCfg {
   static constexpr int REGS_EPILOGUE = 224;
   static_assert(128 * REGS_CONTROL + 32 * EPI_WARPS * REGS_EPILOGUE <= REGS_LAUNCH * THREADS,
                 "setmaxnreg.inc would wait for registers that never become free");
-  static constexpr int A_BYTES = BM * BK;
+  static constexpr int A_BYTES = A_ROWS_ * BK;
+  static_assert(A_ROWS_ == 128 || ((A_ROWS_ == 16 || A_ROWS_ == 64) && BN_ == 256 && !MULTI_),
+                "short A slots exist for the decode case only");
+  static_assert(A_ROWS_ * BK % 1024 == 0, "stage slots must stay 1 KiB aligned for the 128-byte swizzle");
   static constexpr int B_BYTES = BN_ * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int ISSUERS = 2;                 // MMA issuer warps; issuer p takes the K blocks with index = p (mod 2)
@@ -226,10 +235,10 @@ struct DstMaps {
 // multimem.st to a multicast address, otherwise by TMA stores to up to eight destinations.
 // ROWB: B carries one scale per ROW and K block (the deep-gemm layout) instead of one per
 // 128 x 128 block: the promotion multiplies every accumulator column by its own scale.
-template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false>
+template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false, int A_ROWS = 128>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmArgs& args, const CUtensorMap* dmaps) {
-  using Cfg = TileCfg<BN, MULTI>;
+  using Cfg = TileCfg<BN, MULTI, A_ROWS>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
 
@@ -717,6 +726,14 @@ __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
   gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
+}
+
+// Decode forms: 16-row A slots and six pipeline stages (M <= 16), 64-row slots and five (M <= 64).
+template <int BN, int A_ROWS>
+__global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
+gemm_tile_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmArgs args) {
+  gemm_tile_body<BN, false, false, false, false, A_ROWS>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Row-scaled B (deep-gemm layout): single destination, 128-wide tiles.

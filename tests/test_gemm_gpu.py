@@ -283,3 +283,23 @@ def test_fp8_linear_public_wrapper(device):
     qa, sa = oracle.quant_act(x.reshape(-1, 512))
     ref = oracle.gemm_dequant(qa, Bq, sa, Bs)
     assert oracle.bf16_ulp_error(y.reshape(-1, 256).cpu(), ref) <= 1
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (9, 1280, 768), (16, 2560, 2048), (17, 512, 1024), (40, 1280, 640),
+                                   (64, 2560, 2048), (65, 512, 1024)])
+def test_decode_forms_with_short_a_slots(device, M, N, K):
+    """M <= 16 and M <= 64 run kernel forms whose A slot holds only 16 / 64 rows (the MMA's other
+    rows read whatever follows in shared memory and land in rows that are never stored): results
+    must be those of the oracle, NaN-free, and rows beyond M of a larger buffer untouched."""
+    A, B, As, Bs = oracle.make_quantised_inputs(M, N, K, seed=11 * M + N + K)
+    ref = oracle.gemm_dequant(A, B, As, Bs)
+    for variant in ("auto", "tile256"):
+        out32 = _run(device, A, B, As, Bs, torch.float32, variant)
+        assert not torch.isnan(out32).any()
+        assert oracle.max_err_over_rms(out32, ref) <= FP32_TOL
+    big = torch.full((M + 3, N), 7.0, dtype=torch.bfloat16, device=device)
+    runtime.gemm(*_dev((A, B, As, Bs), device), 128, 128, torch.bfloat16, out=big[:M])
+    torch.cuda.synchronize()
+    assert oracle.bf16_ulp_error(big[:M].cpu(), ref) <= 1
+    assert bool((big[M:] == 7.0).all())
+    runtime.check_device_status()
