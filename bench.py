@@ -209,6 +209,9 @@ def extra_shapes(dev, peaks):
         gbs = byts / ms / 1e6
         out[f"decode_M{m}_N28672_K8192"] = {"ms": round(ms, 5), "gbs": round(gbs, 1),
                                             "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+        if m == 256:   # near the ridge: the tensor-side fraction beside the bandwidth-side one
+            tf = 2.0 * m * n * k / ms / 1e9
+            out[f"decode_M{m}_N28672_K8192"].update({"tflops": round(tf, 1), "frac_of_fp8_peak": round(tf / fp8_peak, 3)})
         del a, b, sa, sb, c
     # the same GEMM with one B scale per ROW of B (deep-gemm-helion's operand layout)
     m, n, k = 4096, 4096, 8192

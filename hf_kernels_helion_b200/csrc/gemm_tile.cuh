@@ -548,23 +548,21 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
           for (int j = 0; j < Cfg::EPI_COLS; j += 4)
             *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
         }
-      } else if (MULTI && MC) {
-        // Multicast destination: stage 128 bytes of each of the warp's 32 rows (same swizzle as
-        // below), then eight lanes per row read the row back as 16-byte chunks, so that every
-        // 128-byte row segment leaves as one contiguous multimem.st request.
+      } else if (MULTI && (MC || args.staged_store)) {
+        // Multi-destination and multicast forms: per pass, 128 bytes of each of this warp's 32 rows
+        // go to the warp's staging area in the SWIZZLE_128B pattern (16-byte chunk index XOR
+        // row % 8, conflict-free for the row-wise writes).
         uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
         const int esize = args.out_fp32 ? 4 : 2;
         const int passes = Cfg::EPI_COLS * esize / 128;
-        const int64_t n_bytes = N * esize;
-        uint8_t* mc_base = reinterpret_cast<uint8_t*>(args.dst[0]);
-        const int64_t ld_bytes = args.dst_ld[0] * esize;
-        for (int p = 0; p < passes; ++p) {
-          __syncwarp();                                // the previous pass has been read back
+        auto stage_pass = [&](int p) {
           if (args.out_fp32) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
               float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
               const int j0 = c * 4;
+              // the pass index is a run-time value, the accumulator index must not be: select
+              // over the unrolled candidates
 #pragma unroll
               for (int pp = 0; pp < Cfg::EPI_COLS / 32; ++pp)
                 if (pp == p) v4 = make_float4(ACC(pp * 32 + j0), ACC(pp * 32 + j0 + 1), ACC(pp * 32 + j0 + 2), ACC(pp * 32 + j0 + 3));
@@ -590,71 +588,45 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
               *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = u;
             }
           }
-          __syncwarp();
-          const int c = lane & 7;
-          const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + c * 16;
-          int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
-          uint8_t* gptr = mc_base + grow * ld_bytes + col_byte;
-          const bool col_ok = col_byte < n_bytes;
+        };
+        if constexpr (MC) {
+          // Multicast destination: eight lanes per row read the staged row back as 16-byte chunks, so
+          // that every 128-byte row segment leaves as one contiguous multimem.st request.
+          const int64_t n_bytes = N * esize;
+          uint8_t* mc_base = reinterpret_cast<uint8_t*>(args.dst[0]);
+          const int64_t ld_bytes = args.dst_ld[0] * esize;
+          for (int p = 0; p < passes; ++p) {
+            __syncwarp();                                // the previous pass has been read back
+            stage_pass(p);
+            __syncwarp();
+            const int c = lane & 7;
+            const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + c * 16;
+            int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
+            uint8_t* gptr = mc_base + grow * ld_bytes + col_byte;
+            const bool col_ok = col_byte < n_bytes;
 #pragma unroll 2
-          for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
-            const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
-            if (col_ok && grow < M) multimem_st_v4(gptr, v);
-          }
-        }
-      } else if (MULTI && !MC && args.staged_store) {
-        // Full tile, multi-destination path: per pass, 128 bytes of each of this warp's 32 rows
-        // go to the warp's staging area in the SWIZZLE_128B pattern (16-byte chunk index XOR
-        // row % 8, conflict-free for the row-wise writes), and one TMA store per destination
-        // ships the 32 x 128-byte box; rows and columns beyond [M, N] are clipped by the TMA.
-        uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
-        const int esize = args.out_fp32 ? 4 : 2;
-        const int cols_per_pass = 128 / esize;
-        const int passes = Cfg::EPI_COLS / cols_per_pass;
-        for (int p = 0; p < passes; ++p) {
-          if (lane == 0) bulk_wait_group_read0();   // the previous box has left the staging buffer
-          __syncwarp();
-          if (args.out_fp32) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              float4 v4;
-              const int j0 = c * 4;
-              // columns of this pass start at p * 32: select with a runtime p over unrolled j
-              v4.x = 0.f; v4.y = 0.f; v4.z = 0.f; v4.w = 0.f;
-#pragma unroll
-              for (int pp = 0; pp < Cfg::EPI_COLS / 32; ++pp)
-                if (pp == p) v4 = make_float4(ACC(pp * 32 + j0), ACC(pp * 32 + j0 + 1), ACC(pp * 32 + j0 + 2), ACC(pp * 32 + j0 + 3));
-              *reinterpret_cast<float4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = v4;
-            }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              uint4 u = make_uint4(0u, 0u, 0u, 0u);
-              const int j0 = c * 8;
-#pragma unroll
-              for (int pp = 0; pp < Cfg::EPI_COLS / 64; ++pp)
-                if (pp == p) {
-                  __nv_bfloat162 v0 = __floats2bfloat162_rn(ACC(pp * 64 + j0), ACC(pp * 64 + j0 + 1));
-                  __nv_bfloat162 v1 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 2), ACC(pp * 64 + j0 + 3));
-                  __nv_bfloat162 v2 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 4), ACC(pp * 64 + j0 + 5));
-                  __nv_bfloat162 v3 = __floats2bfloat162_rn(ACC(pp * 64 + j0 + 6), ACC(pp * 64 + j0 + 7));
-                  u.x = *reinterpret_cast<uint32_t*>(&v0);
-                  u.y = *reinterpret_cast<uint32_t*>(&v1);
-                  u.z = *reinterpret_cast<uint32_t*>(&v2);
-                  u.w = *reinterpret_cast<uint32_t*>(&v3);
-                }
-              *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((c ^ (lane & 7)) << 4)) = u;
+            for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
+              if (col_ok && grow < M) multimem_st_v4(gptr, v);
             }
           }
-          // generic-proxy writes above -> visible to the async proxy, then one lane sends the
-          // box to every destination; the copies run on while the warp goes back to the K loop
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int32_t col_byte = col0 * esize + p * 128;
-            const int32_t row0 = m0 + q * 32;
-            for (int d = 0; d < args.n_dst; ++d) tma_store_2d(&dmaps[d], stage_w, col_byte, row0);
-            bulk_commit_group();
+        } else {
+          // One TMA store per destination ships the 32 x 128-byte box; rows and columns beyond
+          // [M, N] are clipped by the TMA.
+          for (int p = 0; p < passes; ++p) {
+            if (lane == 0) bulk_wait_group_read0();   // the previous box has left the staging buffer
+            __syncwarp();
+            stage_pass(p);
+            // generic-proxy writes above -> visible to the async proxy, then one lane sends the
+            // box to every destination; the copies run on while the warp goes back to the K loop
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int32_t col_byte = col0 * esize + p * 128;
+              const int32_t row0 = m0 + q * 32;
+              for (int d = 0; d < args.n_dst; ++d) tma_store_2d(&dmaps[d], stage_w, col_byte, row0);
+              bulk_commit_group();
+            }
           }
         }
       } else
