@@ -32,6 +32,39 @@ def shard_weight(B: torch.Tensor, Bs: torch.Tensor, world: int, rank: int, block
     return B[n0:n1], Bs[n0 // block_n:n1 // block_n]
 
 
+# A CUDA IPC handle names a whole allocation and may be opened only once per process: buffers
+# that the caching allocator carved out of one segment share a handle, so mappings are kept
+# here by handle bytes with a use count.
+_ipc_mappings: dict = {}
+
+
+def _ipc_open_shared(lib, handle: bytes) -> int:
+    import ctypes
+
+    from . import _lib
+
+    entry = _ipc_mappings.get(handle)
+    if entry is None:
+        base = ctypes.c_void_p(0)
+        _lib.check(lib.b200fp8_ipc_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(base)), "b200fp8_ipc_open")
+        entry = [int(base.value), 0]
+        _ipc_mappings[handle] = entry
+    entry[1] += 1
+    return entry[0]
+
+
+def _ipc_close_shared(lib, handle: bytes) -> None:
+    import ctypes
+
+    entry = _ipc_mappings.get(handle)
+    if entry is None:
+        return
+    entry[1] -= 1
+    if entry[1] <= 0:
+        lib.b200fp8_ipc_close(ctypes.c_void_p(entry[0]))
+        del _ipc_mappings[handle]
+
+
 class PeerBuffers:
     """One [M, N] output buffer per rank, each mapped into every process of the group
     (CUDA IPC), so that a kernel on any GPU can store into all of them over NVLink.
@@ -67,10 +100,8 @@ class PeerBuffers:
                 if r == self.rank:
                     self._ptrs[r] = self.local.data_ptr()
                     continue
-                base = ctypes.c_void_p(0)
-                _lib.check(lib.b200fp8_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(base)), "b200fp8_ipc_open")
-                self._bases[r] = base
-                self._ptrs[r] = int(base.value) + off
+                self._bases[r] = h
+                self._ptrs[r] = _ipc_open_shared(lib, h) + off
         dist.barrier(group)
 
     def ptr(self, r: int) -> int:
@@ -101,8 +132,8 @@ class PeerBuffers:
         torch.cuda.synchronize()
         dist.barrier(self.group)          # nobody may still be storing into a buffer that is about to be unmapped
         lib = _lib.load()
-        for base in self._bases.values():
-            lib.b200fp8_ipc_close(base)
+        for h in self._bases.values():
+            _ipc_close_shared(lib, h)
         self._bases = {}
 
 
