@@ -62,7 +62,7 @@ struct GemmArgs {
   // mc_store = 1: dst[0] is a multimem address of a buffer replicated on every GPU of a multicast
   // group; the multi-destination kernel then re-reads each staged box row-wise and writes it
   // with multimem.st, once, and the NVSwitch delivers it to all GPUs (this one included).
-  int a_from_prep;   // 1: A was re-laid by tile_prep_kernel (M < 16 padded to 16 rows), the producer must wait for it
+  int a_from_prep;   // 1: A was re-laid by tile_prep_kernel (M <= 16: 16-row copy), the producer must wait for it
   int n_dst;
   int staged_store;
   int mc_store;
@@ -294,6 +294,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
       if (args.a_from_prep) asm volatile("griddepcontrol.wait;" ::: "memory");
+      const uint64_t pol_stream = policy_evict_first();
+      const uint64_t pol_keep = policy_evict_last();
       uint32_t it = 0;
       bool ok = true;
       SegCursor cur = seg_begin<SK>();
@@ -310,8 +312,14 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
-          tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+          if (A_ROWS < 128 || num_m == 1) {
+            // one M block: the weight is read exactly once, the few activation rows by every CTA
+            tma_load_2d_hint(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0, pol_keep);
+            tma_load_2d_hint(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0, pol_stream);
+          } else {
+            tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
+            tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+          }
           B200FP8_TRACE_EVENT(0, it, 2);
         }
       }
@@ -828,7 +836,7 @@ peer_barrier_kernel(PeerFlags flags, int n, int rank, uint32_t epoch, uint32_t* 
 //   z = 0  AsT[kb][m] = As[m][kb] for m < M, 0 for M <= m < m_pad: 32 x 32 tiles through
 //          shared memory so that both the row-major reads and the K-block-major writes are
 //          coalesced;
-//   z = 1  (only when M < 16) A_pad[16][lda_pad] = A with zero rows appended: TMA boxes over a
+//   z = 1  (only when M <= 16) A_pad[16][lda_pad] = A with zero rows appended: TMA boxes over a
 //          tensor of fewer than 16 rows measured ~20 % slower on B200 than over 16 rows.
 __global__ void __launch_bounds__(256)
 tile_prep_kernel(const float* __restrict__ As, float* __restrict__ AsT, int64_t M, int64_t m_pad, int num_kb,

@@ -113,7 +113,9 @@ def test_workspace_and_variant_queries(lib):
     assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == T256
     assert lib.b200fp8_gemm_pick_variant(16, 128, 512) == T128
     # 112 tiles on 148 SMs: the tail cannot be split in two, the variant degenerates to plain tiles
-    assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4
+    # (K-block-major scales + the 16-row copy of A that M <= 16 goes through)
+    assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4 + 16 * 8192
+    assert lib.b200fp8_gemm_workspace_bytes(17, 28672, 8192, TSK) == 64 * 128 * 4
     assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256, 4)
 
 
