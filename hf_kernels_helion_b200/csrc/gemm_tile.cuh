@@ -465,9 +465,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         return true;
       };
 
-      // One K block: wait for its partial in TMEM, pull it into registers in 32-column
-      // chunks with two tcgen05.ld in flight, hand the TMEM stage back as soon as the last
-      // chunk has landed (before its FMAs).
+      // One K block: wait for its partial in TMEM, pull it into registers (256-wide tile: two
+      // 64-column loads; 128-wide tile: two 32-column loads in flight), hand the TMEM stage
+      // back as soon as the last load has landed (before its FMAs).
       auto promote = [&](float sc) -> bool {
         const uint32_t ts = it % TS;
         const uint32_t tph = (it / TS) & 1u;
@@ -479,6 +479,24 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_col + ts * BN;
+        if constexpr (CHUNKS == 4) {
+          // 256-wide tile: two 64-column loads, each followed by its 64 FMAs; the stage goes back
+          // when the second has landed. Half the tcgen05.ld instructions of the 32-column form.
+          uint32_t p[64];
+          tmem_ld_32x64(taddr, p);
+          tmem_ld_wait_64(p);
+          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
+          fma64_scalar(acc[0], acc[1], p, sc);
+          tmem_ld_32x64(taddr + 64, p);
+          tmem_ld_wait_64(p);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[ts]);
+          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
+          fma64_scalar(acc[2 % CHUNKS], acc[3 % CHUNKS], p, sc);
+          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
+          return true;
+        }
         uint32_t pa[32], pb[32];
         tmem_ld_32x32(taddr, pa);
         tmem_ld_32x32(taddr + 32, pb);
