@@ -424,7 +424,7 @@ def main_ours(args):
                   4: "gemm_tile_kernel<256> with tail split-K"}[variant]
         # DRAM traffic of one GEMM launch: ncu capture of the 1-GPU launch (profiles/), scaled by the
         # fraction of the weight and output this rank touches (A is read whole by every rank)
-        traffic_1gpu = {"read": 342.9e6, "write": 279.8e6}   # profiles/gemm_tile256_c5_8192x18432x7168.md
+        traffic_1gpu = {"read": 343.1e6, "write": 283.9e6}   # profiles/gemm_tile256_c5_8192x18432x7168.md
         traffic = None
         if traffic_1gpu is not None:
             traffic = (M * K + (traffic_1gpu["read"] - M * K) / world) + traffic_1gpu["write"] / world
