@@ -13,7 +13,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libb200fp8.so"
 
 OUT_BF16, OUT_FP32 = 0, 1
 VARIANT_AUTO, VARIANT_TILE128, VARIANT_TILE256, VARIANT_STREAMK, VARIANT_TILE256_SK = 0, 1, 2, 3, 4
-VARIANT_NAMES = {"auto": 0, "tile128": 1, "tile256": 2, "streamk": 3, "tile256_sk": 4}
+VARIANT_PAIR256, VARIANT_PAIR256_SPLIT = 5, 6
+VARIANT_NAMES = {"auto": 0, "tile128": 1, "tile256": 2, "streamk": 3, "tile256_sk": 4, "pair256": 5, "pair256_split": 6}
 
 # name -> (restype, argtypes); mirrors include/b200fp8.h one to one
 SIGNATURES = {
@@ -39,11 +40,13 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t,
                                      c_void_p, c_void_p]),
     "b200fp8_peer_barrier": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p, c_void_p]),
+    "b200fp8_peer_barrier_limited": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),
     "b200fp8_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "b200fp8_ipc_open": (c_int, [c_void_p, c_void_p]),
     "b200fp8_ipc_close": (c_int, [c_void_p]),
     "b200fp8_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
     "b200fp8_gemm_pick_variant": (c_int, [c_int64, c_int64, c_int64]),
+    "b200fp8_gemm_pair_clusters": (c_int, []),
     "b200fp8_gemm_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b200fp8_streamk_first_unit": (c_int64, [c_int64, c_int64, c_int64]),

@@ -24,6 +24,7 @@ struct DeviceInfo {
   std::atomic<int> ready{0};
   int cc_major = 0;
   int sm_count = 0;
+  int pair_clusters = 0;   // CTA pairs of the pair kernels that can be resident at once
 };
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mutex;
@@ -87,6 +88,40 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256, false>::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
+      using PairCfg = TileCfg<256, false, 128, 1>;
+      using PairMultiCfg = TileCfg<256, true, 128, 1>;
+      opt_in(reinterpret_cast<const void*>(&gemm_pair_kernel<false>), PairCfg::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_pair_kernel<true>), PairCfg::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<false>), PairMultiCfg::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<true>), PairMultiCfg::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_pair_kernel<false>), PairCfg::THREADS,
+              128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_pair_kernel<true>), PairCfg::THREADS,
+              128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<false>), PairCfg::THREADS,
+              128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<true>), PairCfg::THREADS,
+              128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
+      if (ok) {
+        // how many CTA pairs fit on the device at once (one CTA per SM; not every SM need be pairable)
+        cudaLaunchAttribute cattr[1];
+        cattr[0].id = cudaLaunchAttributeClusterDimension;
+        cattr[0].val.clusterDim.x = 2;
+        cattr[0].val.clusterDim.y = 1;
+        cattr[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t ccfg = {};
+        ccfg.gridDim = dim3(static_cast<unsigned>(d.sm_count & ~1));
+        ccfg.blockDim = dim3(PairCfg::THREADS);
+        ccfg.dynamicSmemBytes = PairMultiCfg::SMEM_BYTES;
+        ccfg.attrs = cattr;
+        ccfg.numAttrs = 1;
+        int n_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_pair_multi_kernel<true>, &ccfg) != cudaSuccess) {
+          cudaGetLastError();
+          n_clusters = 0;
+        }
+        d.pair_clusters = n_clusters < d.sm_count / 2 ? n_clusters : d.sm_count / 2;
+      }
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<16>), StreamKCfg<16>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<32>), StreamKCfg<32>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_streamk_kernel<64>), StreamKCfg<64>::SMEM_BYTES);
@@ -331,6 +366,54 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   return launch_status();
 }
 
+// CTA-pair kernels: 256 x 256 tiles, one cluster of two CTAs per tile, persistent over the pairs that
+// fit on the device. The B map's box is this CTA's share of the B rows of one MMA.
+template <bool SPLIT>
+int launch_pair(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb, int pair_clusters,
+                cudaStream_t stream) {
+  if (pair_clusters < 1) return B200FP8_ERR_LAUNCH;
+  CUtensorMap ta, tb;
+  int st = make_tmap_u8(&ta, A, args.M, args.K, lda, 128);
+  if (st != B200FP8_OK) return st;
+  st = make_tmap_u8(&tb, B, args.N, args.K, ldb, SPLIT ? 64 : 128);
+  if (st != B200FP8_OK) return st;
+  const int64_t tiles = ((args.M + 255) / 256) * ((args.N + 255) / 256);
+  const int pairs = static_cast<int>(tiles < pair_clusters ? tiles : pair_clusters);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(TileCfg<256, false>::THREADS);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaError_t err;
+  if (args.n_dst > 1) {
+    DstMaps dm;
+    const int64_t esize = args.out_fp32 ? 4 : 2;
+    for (int d = 0; d < 8; ++d) {
+      const int src = d < args.n_dst ? d : 0;
+      st = make_tmap_u8(&dm.m[d], args.dst[src], args.M, args.N * esize, args.dst_ld[src] * esize, 32);
+      if (st != B200FP8_OK) return st;
+    }
+    cfg.dynamicSmemBytes = TileCfg<256, true, 128, 1>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_pair_multi_kernel<SPLIT>, ta, tb, args, dm);
+  } else {
+    cfg.dynamicSmemBytes = TileCfg<256, false, 128, 1>::SMEM_BYTES;
+    err = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<SPLIT>, ta, tb, args);
+  }
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP8_ERR_LAUNCH;
+  }
+  return launch_status();
+}
+
 template <int MP>
 int launch_streamk(const void* A, const void* B, const StreamKArgs& args, int64_t lda, int64_t ldb, int64_t grid,
                    cudaStream_t stream) {
@@ -423,13 +506,24 @@ int64_t b200fp8_streamk_grid(int64_t M, int64_t N, int64_t K) {
   return streamk_plan(M, N, K, sm_count_or_default()).grid;
 }
 
+int b200fp8_gemm_pair_clusters(void) {
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d) != B200FP8_OK) {
+    cudaGetLastError();
+    return 0;
+  }
+  return d->pair_clusters;
+}
+
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) { return pick_variant(M, N, K, sm_count_or_default()); }
 
 int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   const int sms = sm_count_or_default();
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
-  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return tile_workspace_bytes(M, K);
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
+      variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
+    return tile_workspace_bytes(M, K);
   if (variant == B200FP8_VARIANT_TILE256_SK) {
     if (M == 0 || N == 0 || K == 0) return 0;
     const TileSkPlan p = tile_sk_plan(M, N, K, sms);
@@ -466,7 +560,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   const int64_t ldc = dst_ld[0];
   if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
   if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
-  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_TILE256_SK) return B200FP8_ERR_VARIANT;
+  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_PAIR256_SPLIT) return B200FP8_ERR_VARIANT;
   if (M == 0 || N == 0) return B200FP8_OK;
   for (int d = 0; d < n_dst; ++d) {
     if (dst[d] == nullptr) return B200FP8_ERR_NULL;
@@ -519,8 +613,11 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   if (fq.rowb) variant = B200FP8_VARIANT_TILE128;   // the row-scaled promotion exists for the 128-wide tile only
   const bool multi = n_dst > 1 || mc;
   if (fq.rowb && (multi || fused_q)) return B200FP8_ERR_VARIANT;
+  const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT;
+  if (pair && (mc || fq.rowb)) return B200FP8_ERR_VARIANT;
   if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
-  if (multi && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256) return B200FP8_ERR_VARIANT;
+  if (multi && !pair && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256)
+    return B200FP8_ERR_VARIANT;
 
   TileSkPlan skp = {};
   if (variant == B200FP8_VARIANT_TILE256_SK) {
@@ -529,7 +626,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   }
 
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
-      variant == B200FP8_VARIANT_TILE256_SK) {
+      variant == B200FP8_VARIANT_TILE256_SK || pair) {
     const bool sk = variant == B200FP8_VARIANT_TILE256_SK;
     const int64_t prefix = fused_q ? linear_prefix_bytes(M, K) : tile_workspace_bytes(M, K);
     const int64_t need = prefix + (sk ? skp.partial_bytes : 0) + (fq.rowb ? bst_bytes(N, K) : 0);
@@ -586,9 +683,6 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
     args.ldc = ldc;
     args.out_fp32 = out_dtype == B200FP8_OUT_FP32;
     args.status_word = status_word;
-#ifdef B200FP8_TRACE
-    args.trace = reinterpret_cast<long long*>(status_word) + 1;  // trace builds: event buffer follows the status word
-#endif
     const void* a_eff = a_pad ? static_cast<const void*>(a_pad) : A;
     const int64_t lda_eff = a_pad ? align_up(K, 16) : lda;
     if (sk) {
@@ -600,6 +694,10 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
                                                          skp.full, skp.split, skp.kb_per);
       return launch_status();
     }
+    if (variant == B200FP8_VARIANT_PAIR256)
+      return launch_pair<false>(a_eff, B, args, lda_eff, ldb, dev->pair_clusters, stream);
+    if (variant == B200FP8_VARIANT_PAIR256_SPLIT)
+      return launch_pair<true>(a_eff, B, args, lda_eff, ldb, dev->pair_clusters, stream);
     return variant == B200FP8_VARIANT_TILE128 ? launch_tile<128>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream)
                                               : launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream);
   }
@@ -691,7 +789,9 @@ int64_t b200fp8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int vari
   if (M == 0 || N == 0 || K == 0) return 0;
   const int sms = sm_count_or_default();
   if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
-  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256) return linear_prefix_bytes(M, K);
+  if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
+      variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
+    return linear_prefix_bytes(M, K);
   if (variant == B200FP8_VARIANT_TILE256_SK) return linear_prefix_bytes(M, K) + tile_sk_plan(M, N, K, sms).partial_bytes;
   return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
 }
@@ -762,17 +862,23 @@ int b200fp8_ipc_close(void* base) {
   return B200FP8_OK;
 }
 
-int b200fp8_peer_barrier(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch, uint32_t* status_word,
-                         void* stream) {
+int b200fp8_peer_barrier_limited(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch, int64_t limit_clocks,
+                                 uint32_t* status_word, void* stream) {
   if (flag_arrays == nullptr) return B200FP8_ERR_NULL;
-  if (n < 1 || n > 8 || rank < 0 || rank >= n) return B200FP8_ERR_SHAPE;
+  if (n < 1 || n > 8 || rank < 0 || rank >= n || limit_clocks < 1) return B200FP8_ERR_SHAPE;
   PeerFlags f;
   for (int i = 0; i < 8; ++i) {
     f.p[i] = i < n ? flag_arrays[i] : nullptr;
     if (i < n && (f.p[i] == nullptr || (reinterpret_cast<uintptr_t>(f.p[i]) & 3u) != 0)) return B200FP8_ERR_NULL;
   }
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, epoch, status_word);
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, n, rank, epoch,
+                                                                       static_cast<long long>(limit_clocks), status_word);
   return launch_status();
+}
+
+int b200fp8_peer_barrier(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch, uint32_t* status_word,
+                         void* stream) {
+  return b200fp8_peer_barrier_limited(flag_arrays, n, rank, epoch, kPeerBarrierDefaultLimitClks, status_word, stream);
 }
 
 int b200fp8_gemm_decode_static(const void* A, const void* B, const float* As, const float* Bs, void* C, int64_t M,

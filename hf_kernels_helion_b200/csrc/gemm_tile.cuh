@@ -24,18 +24,6 @@
 
 namespace b200fp8 {
 
-// Optional event trace for performance work (compiled in only with -DB200FP8_TRACE):
-// CTA 0 records clock64 stamps of its role loops for K-block indices [40, 56).
-#ifdef B200FP8_TRACE
-#define B200FP8_TRACE_EVENT(role, idx, tag)                                                          \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) >= 40u && (idx) < 56u && args.trace)     \
-      args.trace[((role) * 16 + ((idx) - 40u)) * 8 + (tag)] = clock64();                              \
-  } while (0)
-#else
-#define B200FP8_TRACE_EVENT(role, idx, tag) do { } while (0)
-#endif
-
 // Even split of `total` work units over `grid` owners in contiguous ranges: owner c has
 // units [streamk_first_unit(c), streamk_first_unit(c + 1)).
 __host__ __device__ __forceinline__ int64_t streamk_first_unit(int64_t c, int64_t total, int64_t grid) {
@@ -82,9 +70,6 @@ struct GemmArgs {
   int64_t ld_as, ld_bs, ldc;
   int out_fp32;
   uint32_t* status_word;
-#ifdef B200FP8_TRACE
-  long long* trace;
-#endif
 };
 
 // A_ROWS_: rows of A that the TMA actually brings in per K block (128; 16 or 64 for decode shapes
@@ -92,13 +77,25 @@ struct GemmArgs {
 // (2 or 8 KiB) the remaining rows alias the B tile that follows it in the same stage - garbage
 // that lands in accumulator rows which are never stored - and the bytes saved buy one or two
 // more pipeline stages (weight streaming is bound by the bytes in flight per SM).
-template <int BN_, bool MULTI_ = false, int A_ROWS_ = 128>
+// PAIR_: 0 = one CTA per tile. 1, 2 = CTA pairs (clusters of two, tcgen05 cta_group::2): a pair owns
+// a 256 x BN tile, each CTA accumulates its 128 rows in its own TMEM and holds its 128 rows of A and
+// HALF of the B rows of the tile in shared memory (the MMA reads B from both CTAs), so a K block costs
+// each SM 32 KiB of shared-memory fill and read instead of 48. PAIR_ = 2 additionally issues every K
+// block as two 128-column halves with a TMEM-full / TMEM-empty barrier pair each: the promotion of
+// columns 0..127 starts when the first half of the MMAs has retired and its TMEM columns are handed
+// back a half block earlier, which shortens the accumulator round trip that bounds the kernel.
+template <int BN_, bool MULTI_ = false, int A_ROWS_ = 128, int PAIR_ = 0>
 struct TileCfg {
-  static constexpr int BM = 128;
+  static constexpr int BM = 128;                          // rows per CTA
+  static constexpr int PAIR = PAIR_;
+  static constexpr int TILE_M = PAIR_ ? 256 : 128;        // rows per worker (CTA or CTA pair)
   static constexpr int BN = BN_;
   static constexpr int BK = 128;  // fp8 elements = bytes = one 128-byte swizzle span
   static constexpr int A_ROWS = A_ROWS_;
-  static constexpr int STAGES = (A_ROWS_ == 16) ? 6 : (A_ROWS_ == 64) ? 5 : (BN_ == 128) ? 6 : 4;
+  static constexpr int HALVES = PAIR_ == 2 ? 2 : 1;       // separately signalled column halves of a K block
+  static constexpr int B_ROWS = PAIR_ ? BN_ / 2 : BN_;    // rows of B per CTA and K block
+  static constexpr int STAGES = PAIR_ ? 6 : (A_ROWS_ == 16) ? 6 : (A_ROWS_ == 64) ? 5 : (BN_ == 128) ? 6 : 4;
+  static_assert(PAIR_ == 0 || (BN_ == 256 && A_ROWS_ == 128), "pair kernels: 256-wide tiles, full A slots");
   static constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quarter
   static constexpr int EPI_COLS = BN_ / 2;          // accumulator columns (registers) per epilogue thread
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
@@ -124,7 +121,7 @@ struct TileCfg {
   static_assert(A_ROWS_ == 128 || ((A_ROWS_ == 16 || A_ROWS_ == 64) && BN_ == 256 && !MULTI_),
                 "short A slots exist for the decode case only");
   static_assert(A_ROWS_ * BK % 1024 == 0, "stage slots must stay 1 KiB aligned for the 128-byte swizzle");
-  static constexpr int B_BYTES = BN_ * BK;
+  static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int ISSUERS = 2;                 // MMA issuer warps; issuer p takes the K blocks with index = p (mod 2)
   static constexpr int TMEM_STAGES = 512 / BN_;     // accumulator stages in TMEM (all 512 columns are used)
@@ -160,24 +157,29 @@ struct Segment {
   bool first;   // first segment of this CTA
 };
 
+// A worker is one CTA, or one CTA pair in the pair kernels (both CTAs of a pair walk the same list).
 struct SegCursor {
   int tile;          // next whole tile of the round-robin part
-  bool tail_done;    // the tail range of this CTA (SK kernels) has been handed out
+  int worker, nworkers;
+  bool tail_done;    // the tail range of this worker (SK kernels) has been handed out
   bool started;
 };
 
 template <bool SK>
-__device__ __forceinline__ SegCursor seg_begin() {
+__device__ __forceinline__ SegCursor seg_begin(int worker, int nworkers) {
   SegCursor c;
-  c.tile = static_cast<int>(blockIdx.x);
+  c.tile = worker;
+  c.worker = worker;
+  c.nworkers = nworkers;
   c.tail_done = false;
   c.started = false;
   return c;
 }
 
 // The tail range of this CTA: false if it has none.
-__device__ __forceinline__ bool seg_tail(const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles, Segment& s) {
-  const int u = static_cast<int>(blockIdx.x);
+__device__ __forceinline__ bool seg_tail(const GemmArgs& a, int worker, int num_m, int num_n, int num_kb, int num_tiles,
+                                         Segment& s) {
+  const int u = worker;
   const int tail_tiles = num_tiles - a.sk_full;
   if (u >= tail_tiles * a.sk_split) return false;
   const int t = a.sk_full + u / a.sk_split;
@@ -190,15 +192,15 @@ __device__ __forceinline__ bool seg_tail(const GemmArgs& a, int num_m, int num_n
 
 // Number of K blocks this CTA processes in total.
 template <bool SK>
-__device__ __forceinline__ uint32_t seg_total_kblocks(const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles) {
+__device__ __forceinline__ uint32_t seg_total_kblocks(const GemmArgs& a, int worker, int nworkers, int num_m, int num_n,
+                                                      int num_kb, int num_tiles) {
   const int whole_end = SK ? a.sk_full : num_tiles;
   int mine = 0;
-  if (static_cast<int>(blockIdx.x) < whole_end)
-    mine = (whole_end - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  if (worker < whole_end) mine = (whole_end - worker + nworkers - 1) / nworkers;
   uint32_t total = static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
   if constexpr (SK) {
     Segment s;
-    if (seg_tail(a, num_m, num_n, num_kb, num_tiles, s)) total += static_cast<uint32_t>(s.kb_end - s.kb_begin);
+    if (seg_tail(a, worker, num_m, num_n, num_kb, num_tiles, s)) total += static_cast<uint32_t>(s.kb_end - s.kb_begin);
   }
   return total;
 }
@@ -213,13 +215,13 @@ __device__ __forceinline__ bool seg_next(SegCursor& c, const GemmArgs& a, int nu
     tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
     s.kb_begin = 0;
     s.kb_end = num_kb;
-    c.tile += static_cast<int>(gridDim.x);
+    c.tile += c.nworkers;
     return true;
   }
   if constexpr (SK) {
     if (!c.tail_done) {
       c.tail_done = true;
-      return seg_tail(a, num_m, num_n, num_kb, num_tiles, s);
+      return seg_tail(a, c.worker, num_m, num_n, num_kb, num_tiles, s);
     }
   }
   return false;
@@ -235,12 +237,14 @@ struct DstMaps {
 // multimem.st to a multicast address, otherwise by TMA stores to up to eight destinations.
 // ROWB: B carries one scale per ROW and K block (the deep-gemm layout) instead of one per
 // 128 x 128 block: the promotion multiplies every accumulator column by its own scale.
-template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false, int A_ROWS = 128>
+template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false, int A_ROWS = 128, int PAIR = 0>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmArgs& args, const CUtensorMap* dmaps) {
-  using Cfg = TileCfg<BN, MULTI, A_ROWS>;
+  using Cfg = TileCfg<BN, MULTI, A_ROWS, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
+  constexpr uint32_t H = Cfg::HALVES;
+  static_assert(!(PAIR && (SK || MC || ROWB)), "pair kernels: whole tiles, block scales, plain or TMA-store output");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -248,38 +252,54 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::OUT_STAGE_BYTES);
   uint64_t* full = bars;                  // [STAGES]  TMA bytes landed
   uint64_t* empty = bars + STAGES;        // [STAGES]  MMA finished reading the slot
-  uint64_t* tfull = bars + 2 * STAGES;    // [TS]      TMEM stage holds a finished K-block partial
-  uint64_t* tempty = bars + 2 * STAGES + TS;  // [TS]  every epilogue warp has read the TMEM stage
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * TS);
-  static_assert((2 * STAGES + 2 * TS) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
+  uint64_t* tfull = bars + 2 * STAGES;    // [TS * H]  TMEM stage (half) holds a finished K-block partial
+  uint64_t* tempty = bars + 2 * STAGES + TS * H;  // [TS * H]  every epilogue warp has read the TMEM stage (half)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * TS * H);
+  static_assert((2 * STAGES + 2 * TS * H) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Pair kernels: CTA 0 of the pair (the leader) issues the MMAs for both; its `full` barriers
+  // collect the bytes of both CTAs' loads and its `tempty` barriers the arrivals of both CTAs'
+  // promotion warps. `empty` and `tfull` exist in both CTAs and the leader signals each copy.
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int nworkers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (uint32_t s = 0; s < TS; ++s) {
+    for (uint32_t s = 0; s < TS * H; ++s) {
       mbar_init(&tfull[s], 1);
-      mbar_init(&tempty[s], Cfg::EPI_WARPS);
+      mbar_init(&tempty[s], (Cfg::EPI_WARPS / H) * (PAIR ? 2 : 1));
     }
     *abort_flag = 0u;
     fence_barrier_init();
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) {
+    cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int64_t M = args.M, N = args.N, K = args.K;
-  const int num_m = static_cast<int>((M + Cfg::BM - 1) / Cfg::BM);
+  const int num_m = static_cast<int>((M + Cfg::TILE_M - 1) / Cfg::TILE_M);
   const int num_n = static_cast<int>((N + BN - 1) / BN);
   const int num_kb = static_cast<int>((K + Cfg::BK - 1) / Cfg::BK);
   const int num_tiles = num_m * num_n;
@@ -298,19 +318,35 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       const uint64_t pol_keep = policy_evict_last();
       uint32_t it = 0;
       bool ok = true;
-      SegCursor cur = seg_begin<SK>();
+      SegCursor cur = seg_begin<SK>(worker, nworkers);
       Segment seg;
+      const uint32_t full_leader = PAIR ? mapa_shared(smem_u32(full), 0u) : 0u;
       while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
-        const int m0 = seg.m_blk * Cfg::BM;
+        const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
         const int n0 = seg.n_blk * BN;
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          B200FP8_TRACE_EVENT(0, it, 0);
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status_word)) { ok = false; break; }
-          B200FP8_TRACE_EVENT(0, it, 1);
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          if constexpr (PAIR) {
+            // the leader's barrier counts the bytes of both CTAs' copies of this stage
+            if (leader) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+            const uint32_t fb = full_leader + s * 8u;
+            tma_load_2d_pair(a_dst, &tmap_a, fb, kb * Cfg::BK, m0);
+            if constexpr (PAIR == 1) {
+              // B rows of the whole 256-column MMA: this CTA's half
+              tma_load_2d_pair(b_dst, &tmap_b, fb, kb * Cfg::BK, n0 + static_cast<int>(cta_rank) * 128);
+            } else {
+              // two 128-column MMAs per K block: this CTA's 64 rows of each
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+                tma_load_2d_pair(b_dst + h * 64 * Cfg::BK, &tmap_b, fb, kb * Cfg::BK,
+                                 n0 + h * 128 + static_cast<int>(cta_rank) * 64);
+            }
+            continue;
+          }
           mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
           if (A_ROWS < 128 || num_m == 1) {
             // one M block: the weight is read exactly once, the few activation rows by every CTA
@@ -320,11 +356,11 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
             tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
             tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
           }
-          B200FP8_TRACE_EVENT(0, it, 2);
         }
       }
-      if (!ok) {
-        // Abort path: let this CTA's own copies in flight land before shared memory is released.
+      if (!ok && leader) {
+        // Abort path: let this CTA's own copies in flight land before shared memory is released
+        // (pair kernels: the peer's copies are covered by the cluster barrier at the end).
         const uint32_t first = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
         for (uint32_t j = first; j < it; ++j) {
           const uint64_t t0 = globaltimer_ns();
@@ -334,7 +370,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {
+  } else if ((warp == 1 || warp == 3) && leader) {
     // ------------------------------------------------------------------ MMA issuers
     // Issuing the four tcgen05.mma of a K block, the two commits and the two barrier waits
     // costs an issuer some 650 clocks, while the tensor pipe needs 512 (BN = 256) or 256
@@ -342,13 +378,19 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     // K blocks whose running index is p (mod 2). Consecutive K blocks use different smem
     // slots and different TMEM stages, so the two instruction streams are independent.
     // The whole warp runs the loop (addresses stay warp-uniform) and one elected lane issues.
+    // Pair kernels: only the leader CTA issues; every commit is sent twice, once to each CTA's
+    // copy of the barrier.
     const uint32_t p = (warp == 1) ? 0u : 1u;
-    constexpr uint32_t idesc = make_idesc_e4m3_f32(128, BN);
+    constexpr uint32_t idesc = make_idesc_e4m3_f32(Cfg::TILE_M, BN / H);
     const uint32_t smem_base = smem_u32(smem);
+    const uint32_t empty_own = PAIR ? mapa_shared(smem_u32(empty), 0u) : 0u;
+    const uint32_t empty_peer = PAIR ? mapa_shared(smem_u32(empty), 1u) : 0u;
+    const uint32_t tfull_own = PAIR ? mapa_shared(smem_u32(tfull), 0u) : 0u;
+    const uint32_t tfull_peer = PAIR ? mapa_shared(smem_u32(tfull), 1u) : 0u;
     uint32_t it = 0;
     uint32_t last = 0xffffffffu;
     bool ok = true;
-    const uint32_t total_it = seg_total_kblocks<SK>(args, num_m, num_n, num_kb, num_tiles);
+    const uint32_t total_it = seg_total_kblocks<SK>(args, worker, nworkers, num_m, num_n, num_kb, num_tiles);
     {
       for (; it < total_it; ++it) {
         if ((it & 1u) != p) continue;
@@ -362,31 +404,46 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         const uint64_t a_desc = make_smem_desc_sw128(a_addr);
         const uint64_t b_desc = make_smem_desc_sw128(a_addr + Cfg::A_BYTES);
         const uint32_t d_tmem = tmem_base + ts * BN;
-        B200FP8_TRACE_EVENT(1, it, 0);
         ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, abort_flag, status_word));
-        B200FP8_TRACE_EVENT(1, it, 1);
-        ok = ok && __all_sync(0xffffffffu, mbar_wait(&tempty[ts], tph ^ 1u, abort_flag, status_word));
-        B200FP8_TRACE_EVENT(1, it, 2);
         if (!ok) break;
-        tc_fence_after();
-        if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < Cfg::BK / 32; ++k) {
-            // +2 in the start-address field = +32 bytes = one K=32 slice of e4m3
-            umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+        for (uint32_t h = 0; h < H; ++h) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&tempty[ts * H + h], tph ^ 1u, abort_flag, status_word));
+          if (!ok) break;
+          tc_fence_after();
+          if (elect_one()) {
+            if constexpr (PAIR) {
+              // half h: this CTA's 64 (or, H = 1, 128) B rows sit h * 8 KiB into the B slot
+              const uint64_t bh = b_desc + ((h * 64u * Cfg::BK) >> 4);
+#pragma unroll
+              for (int k = 0; k < Cfg::BK / 32; ++k)
+                umma_f8_pair(d_tmem + h * (BN / H), a_desc + 2u * k, bh + 2u * k, idesc, k > 0 ? 1u : 0u);
+              if (h + 1 == H) {
+                tc_commit_pair(empty_own + s * 8u);
+                tc_commit_pair(empty_peer + s * 8u);
+              }
+              tc_commit_pair(tfull_own + (ts * H + h) * 8u);
+              tc_commit_pair(tfull_peer + (ts * H + h) * 8u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < Cfg::BK / 32; ++k) {
+                // +2 in the start-address field = +32 bytes = one K=32 slice of e4m3
+                umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+              }
+              tc_commit(&empty[s]);
+              tc_commit(&tfull[ts]);
+            }
           }
-          tc_commit(&empty[s]);
-          tc_commit(&tfull[ts]);
+          __syncwarp();
         }
-        __syncwarp();
-        B200FP8_TRACE_EVENT(1, it, 3);
+        if (!ok) break;
         last = it;
       }
     }
     if (!ok && last != 0xffffffffu && lane == 0) {
       // Abort path: bounded wait for the MMAs this warp already issued.
       const uint64_t t0 = globaltimer_ns();
-      while (!mbar_try_wait(&tfull[last % TS], (last / TS) & 1u)) {
+      while (!mbar_try_wait(&tfull[(last % TS) * H + H - 1], (last / TS) & 1u)) {
         if (globaltimer_ns() - t0 > kWaitLimitNs) break;
       }
     }
@@ -404,10 +461,21 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     // the scale copy AsT is written by the preceding tile_prep_kernel; with programmatic
     // dependent launch this kernel may have started before that grid finished
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    SegCursor cur = seg_begin<SK>();
+    // TMEM-full / TMEM-empty barrier of this warp's columns inside TMEM stage ts: index ts * H + hb
+    const uint32_t hb = (H == 2) ? static_cast<uint32_t>(cw) : 0u;
+    const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0u) : 0u;
+    auto release_stage = [&](uint32_t bar_idx) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(tempty_leader + bar_idx * 8u);
+        else mbar_arrive(&tempty[bar_idx]);
+      }
+    };
+    SegCursor cur = seg_begin<SK>(worker, nworkers);
     Segment seg;
     while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
-      const int m0 = seg.m_blk * Cfg::BM;
+      const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
       const int n0 = seg.n_blk * BN;
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
       const int col0 = n0 + cw * Cfg::EPI_COLS;
@@ -471,12 +539,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       auto promote = [&](float sc) -> bool {
         const uint32_t ts = it % TS;
         const uint32_t tph = (it / TS) & 1u;
-        const uint32_t tr_it = it, tr_role = (warp == 4) ? 2u : ((warp == 8) ? 3u : 99u);
-        (void)tr_it; (void)tr_role;
         ++it;
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 0);
-        if (!__all_sync(0xffffffffu, mbar_wait(&tfull[ts], tph, abort_flag, status_word))) return false;
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tfull[ts * H + hb], tph, abort_flag, status_word))) return false;
         tc_fence_after();
         const uint32_t taddr = tmem_base + lane_col + ts * BN;
         if constexpr (CHUNKS == 4) {
@@ -485,16 +549,11 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
           uint32_t p[64];
           tmem_ld_32x64(taddr, p);
           tmem_ld_wait_64(p);
-          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
           fma64_scalar(acc[0], acc[1], p, sc);
           tmem_ld_32x64(taddr + 64, p);
           tmem_ld_wait_64(p);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty[ts]);
-          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
+          release_stage(ts * H + hb);
           fma64_scalar(acc[2 % CHUNKS], acc[3 % CHUNKS], p, sc);
-          if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
           return true;
         }
         uint32_t pa[32], pb[32];
@@ -502,16 +561,10 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         tmem_ld_32x32(taddr + 32, pb);
         tmem_ld_wait_32(pa);
         tmem_ld_wait_32(pb);
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 2);
 #pragma unroll
         for (int g = 0; g < CHUNKS; g += 2) {
           const bool more = g + 2 < CHUNKS;
-          if (!more) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[ts]);
-            if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 3);
-          }
+          if (!more) release_stage(ts * H + hb);
           fma32_scalar(acc[g], pa, sc);
           if (more) tmem_ld_32x32(taddr + (g + 2) * 32, pa);
           fma32_scalar(acc[g + 1], pb, sc);
@@ -521,7 +574,6 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
             tmem_ld_wait_32(pb);
           }
         }
-        if (tr_role < 4u) B200FP8_TRACE_EVENT(tr_role, tr_it, 4);
         return true;
       };
 
@@ -703,10 +755,16 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   }
   __syncwarp();
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) {
+    // neither CTA may leave (its shared memory and TMEM are read and signalled by the other) before both are done
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -715,6 +773,22 @@ __global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
 gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs args) {
   gemm_tile_body<BN, false, SK>(tmap_a, tmap_b, args, nullptr);
+}
+
+// CTA-pair forms (launch with cluster dimension 2 and an even grid): 256 x 256 tiles per pair.
+// SPLIT = false: one 256-column MMA chain per K block; true: two 128-column halves.
+template <bool SPLIT>
+__global__ void __launch_bounds__(TileCfg<256, false>::THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs args) {
+  gemm_tile_body<256, false, false, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, nullptr);
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(TileCfg<256, true>::THREADS, 1)
+gemm_pair_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
+  gemm_tile_body<256, true, false, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, dmaps.m);
 }
 
 // Multi-destination form: the finished tile is staged in shared memory and sent to every
@@ -774,10 +848,10 @@ tile_prep_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t
     v[0] = __ldg(src);
     v[1] = __ldg(src + 1);
   }
-  float amax = fmaxf(amax8(v[0]), amax8(v[1]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  float amax = fmax_nan(amax8(v[0]), amax8(v[1]));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
   const float scale = scale_of_amax(amax);
   uint2 o[2];
   quant_vecs<2>(v, scale, o);
@@ -824,26 +898,28 @@ tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int6
 // (p < n) stores `epoch` into slot `rank` of GPU p's flag array (a release store at system scope
 // over NVLink), then polls slot p of its own array until GPU p's store of the same epoch has
 // arrived. Epochs only grow, so a late reader never misses one (comparison is wrap-safe).
-// The wait is bounded (~10 s of SM clocks, generous because the ranks' hosts may be seconds
-// apart at start-up); on expiry the status word gets B200FP8_DEV_WAIT_TIMEOUT and the kernel
-// returns. The kernels of different GPUs wait on one another: never run two ranks on one GPU.
+// The wait is bounded by `limit_clocks` SM clocks (default ~10 s, generous because the ranks' hosts
+// may be seconds apart at start-up); on expiry the status word gets B200FP8_DEV_WAIT_TIMEOUT and
+// the kernel returns normally. The kernels of different GPUs wait on one another: never run two
+// ranks on one GPU.
 struct PeerFlags {
   uint32_t* p[8];
 };
 
+constexpr long long kPeerBarrierDefaultLimitClks = 20000000000ll;
+
 __global__ void __launch_bounds__(32)
-peer_barrier_kernel(PeerFlags flags, int n, int rank, uint32_t epoch, uint32_t* status_word) {
+peer_barrier_kernel(PeerFlags flags, int n, int rank, uint32_t epoch, long long limit_clocks, uint32_t* status_word) {
   const int lane = threadIdx.x;
   if (lane >= n) return;
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[lane] + rank), "r"(epoch) : "memory");
   const uint32_t* mine = flags.p[rank] + lane;
   const long long t0 = clock64();
-  constexpr long long kLimit = 20000000000ll;
   for (uint32_t polls = 0;; ++polls) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (static_cast<int32_t>(v - epoch) >= 0) break;
-    if ((polls & 255u) == 255u && clock64() - t0 > kLimit) {
+    if ((polls & 255u) == 255u && clock64() - t0 > limit_clocks) {
       if (status_word != nullptr) atomicOr(status_word, B200FP8_DEV_WAIT_TIMEOUT);
       break;
     }

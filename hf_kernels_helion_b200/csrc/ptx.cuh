@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../../include/b200fp8.h"
+
 namespace b200fp8 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -28,6 +30,26 @@ __device__ __forceinline__ bool elect_one() {
       "}\n"
       : "=r"(pred));
   return pred != 0;
+}
+
+// ----------------------------------------------------------------------------- CTA pairs (clusters of two)
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address, in the cluster's shared window, of the same shared-memory location in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+
+// Barrier over all threads of all CTAs of the cluster (every warp converged).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // Warpgroup-wide register re-allocation (all four warps of an aligned warpgroup
@@ -62,6 +84,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Arrive on an mbarrier given by its address in the cluster's shared window (own or peer CTA).
+// Default (release, CTA scope) semantics: what the arrival orders here are tcgen05.ld reads, which
+// tcgen05.wait::ld and tcgen05.fence::before_thread_sync have already ordered; the .release.cluster
+// form was measured to halve the speed of the pair kernels (it drains the warp's memory traffic).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
@@ -101,45 +131,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         t0 = now;
       } else if (now - t0 > kWaitLimitClks) {
         *abort_flag = 1u;
-        if (status_word != nullptr) atomicExch(status_word, 1u);
+        if (status_word != nullptr) atomicOr(status_word, B200FP8_DEV_WAIT_TIMEOUT);
         return false;
       }
     }
   }
-}
-
-// Non-blocking probe of a phase (mbarrier.test_wait). Issued early, its shared-memory round
-// trip overlaps whatever independent work follows; mbar_wait_probed finishes the job.
-__device__ __forceinline__ bool mbar_probe(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Waits that tolerate failure: used by the promotion warps, which after a timeout keep
-// running (every later wait returns at once because the abort flag is up) so that the warp
-// stays converged for its .sync.aligned instructions and the CTA still reaches its teardown;
-// the output is then invalid and the status word says so.
-__device__ __forceinline__ void mbar_wait_probed(bool probed_ready, uint64_t* bar, uint32_t parity,
-                                                 volatile uint32_t* abort_flag, uint32_t* status_word) {
-  if (!probed_ready && *abort_flag == 0u) (void)mbar_wait(bar, parity, abort_flag, status_word);
-}
-
-// Warp-wide wait: lane 0 polls, the result is broadcast (one mbarrier transaction per
-// poll instead of 32). Must be called by all 32 lanes.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                               uint32_t* status_word) {
-  uint32_t ok = 1u;
-  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, abort_flag, status_word) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
 }
 
 // ----------------------------------------------------------------------------- TMA (tiled, 2-D, no multicast)
@@ -154,6 +150,17 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Load issued by either CTA of a pair into its OWN shared memory, completing bytes on an mbarrier
+// that may live in the other CTA of the pair (`bar_cluster_addr`, an address in the cluster's shared
+// window). Not a multicast: the data goes to the issuing CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
+                                                 int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
 
@@ -224,6 +231,39 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+// CTA-pair forms (cta_group::2): both CTAs of the pair execute alloc / relinquish / dealloc; the
+// MMA and its commits are issued by one thread of the leader CTA. A commit arrives on ONE mbarrier,
+// given by its address in the cluster's shared window, when the MMAs issued so far have retired in
+// both CTAs; the issuer sends one commit per CTA that has to hear of it.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+// D (256 x N over the pair: each CTA's TMEM holds its 128 rows) (+)= A . B^T, one K = 32 slice; each
+// CTA supplies its 128 rows of A and its N / 2 rows of B from the same shared-memory offsets.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // D[tmem] (+)= A[smem] . B[smem]^T, e4m3 x e4m3 -> fp32, one K=32 slice.

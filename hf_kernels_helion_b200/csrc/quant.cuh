@@ -21,15 +21,23 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float a, float b) {
   return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
 }
 
-// max |x| over 8 bf16 (one uint4), as fp32; packed bf16x2 abs / max, exact.
+// max(a, b) that returns NaN when either operand is NaN (fmaxf would drop it).
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+// max |x| over 8 bf16 (one uint4), as fp32; packed bf16x2 abs / max, exact. A NaN among the
+// eight comes out as NaN (like torch.amax), so that it reaches the group's scale.
 __device__ __forceinline__ float amax8(const uint4& v) {
   const uint32_t m = 0x7FFF7FFFu;
   uint32_t a = v.x & m, b = v.y & m, c = v.z & m, d = v.w & m;
-  __nv_bfloat162 ab = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  __nv_bfloat162 cd = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&c), *reinterpret_cast<__nv_bfloat162*>(&d));
-  ab = __hmax2(ab, cd);
+  __nv_bfloat162 ab = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  __nv_bfloat162 cd = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&c), *reinterpret_cast<__nv_bfloat162*>(&d));
+  ab = __hmax2_nan(ab, cd);
   const uint32_t w = *reinterpret_cast<uint32_t*>(&ab);
-  return fmaxf(bf16_lo(w), bf16_hi(w));
+  return fmax_nan(bf16_lo(w), bf16_hi(w));
 }
 
 // e4m3(x / scale) without a division per element, bit-identical to the division.
@@ -88,6 +96,8 @@ __device__ __forceinline__ uint2 quant8_div(const uint4& v, float scale) {
 
 // N x 8 bf16 (N uint4) divided by `scale` and packed into N x 8 e4m3 bytes (N uint2).
 // scale == 0 (all-zero group) yields zero bytes instead of the 0/0 NaN of the formula.
+// A NaN scale (a NaN in the group) makes every byte of the group NaN, an infinite one (an Inf in
+// the group) makes finite elements zero and infinite ones NaN: what the formula gives.
 template <int NV>
 __device__ __forceinline__ void quant_vecs(const uint4 (&v)[NV], float scale, uint2 (&o)[NV]) {
   if (scale >= kScaleMinFast && scale <= kScaleMaxFast) {
@@ -120,10 +130,10 @@ quant_act_contig_kernel(const uint4* __restrict__ x, uint4* __restrict__ q, floa
     v[0] = __ldg(x + 2 * t);
     v[1] = __ldg(x + 2 * t + 1);
   }
-  float amax = fmaxf(amax8(v[0]), amax8(v[1]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  float amax = fmax_nan(amax8(v[0]), amax8(v[1]));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
   const float scale = scale_of_amax(amax);
   uint2 o[2];
   quant_vecs<2>(v, scale, o);
@@ -172,10 +182,10 @@ quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, f
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (!in_loop[u]) continue;
-      float amax = fmaxf(amax8(v[u][0]), amax8(v[u][1]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      float amax = fmax_nan(amax8(v[u][0]), amax8(v[u][1]));
+      amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
       const float scale = scale_of_amax(amax);
       uint8_t* dst = q + row[u] * ldq + col[u];
       if (has0[u]) {
@@ -214,15 +224,15 @@ quant_weight_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q
   for (int i = 0; i < 8; ++i) {
     v[i] = make_uint4(0u, 0u, 0u, 0u);
     if (row < N && col0 + i * 8 + 8 <= K) v[i] = __ldg(reinterpret_cast<const uint4*>(w + row * ldw + col0 + i * 8));
-    amax = fmaxf(amax, amax8(v[i]));
+    amax = fmax_nan(amax, amax8(v[i]));
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int o = 16; o > 0; o >>= 1) amax = fmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
   __syncthreads();
   amax = warp_max[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
+  for (int i = 1; i < 8; ++i) amax = fmax_nan(amax, warp_max[i]);
   const float scale = scale_of_amax(amax);
   uint2 o[8];
   quant_vecs<8>(v, scale, o);

@@ -239,7 +239,8 @@ class ShardedFp8Linear:
             dist.all_gather_into_tensor(buf.view(-1), mine.reshape(-1), group=self.group)
         return buf
 
-    def forward_fused(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16) -> torch.Tensor:
+    def forward_fused(self, A: torch.Tensor, As: torch.Tensor, output_dtype=torch.bfloat16,
+                      reader_done: Optional[torch.cuda.Event] = None) -> torch.Tensor:
         """Contiguous C [M, N] on every rank with the exchange fused into the GEMM: the kernel's
         epilogue stores this rank's column slice into the [M, N] buffer of EVERY rank (peer
         stores over NVLink), and a one-warp flag-exchange kernel afterwards (or, with
@@ -247,8 +248,12 @@ class ShardedFp8Linear:
         slices have arrived.  No all-gather, no transpose copy, no NCCL call on the data path.
 
         Two buffer sets alternate between calls: the result returned by call i stays valid until
-        call i + 2 is issued, and work that reads it must be enqueued on the current stream
-        before call i + 1 (whose barrier then orders it before any peer's later overwrite)."""
+        call i + 2 is issued.  Peers start overwriting that buffer once THIS rank has passed the
+        barrier of call i + 1, so every reader of call i's result must be ordered before that
+        barrier: work enqueued on the current stream before call i + 1 is; a reader on ANOTHER
+        stream (a read-back on a copy stream, say) must record an event when it is done and pass
+        it as `reader_done` to call i + 1, which makes the current stream wait for it before the
+        barrier is enqueued."""
         from . import runtime  # noqa: PLC0415
 
         M = A.shape[0]
@@ -269,6 +274,8 @@ class ShardedFp8Linear:
         order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
         ptrs = [pb.ptr(r) + col_bytes for r in order]
         runtime.gemm_scatter(A, self.B, As, self.Bs, ptrs, [self.N] * self.world, output_dtype)
+        if reader_done is not None:
+            torch.cuda.current_stream(A.device).wait_event(reader_done)
         if self.world > 1:
             if self.device_barrier:
                 self._epoch += 1

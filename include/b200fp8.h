@@ -55,6 +55,8 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_TILE256 2 /* persistent tcgen05 kernel, 128x256 output tiles */
 #define B200FP8_VARIANT_STREAMK 3 /* swap-AB stream-K kernel for M <= 256 (decode shapes) */
 #define B200FP8_VARIANT_TILE256_SK 4 /* 128x256 tiles; the tiles of the last, partly empty wave are split along K over the idle SMs */
+#define B200FP8_VARIANT_PAIR256 5 /* 256x256 tiles on CTA pairs (tcgen05 cta_group::2), each SM holds half of the B tile */
+#define B200FP8_VARIANT_PAIR256_SPLIT 6 /* same, every K block issued and promoted as two 128-column halves */
 
 /* codes a kernel may leave in *status_word */
 #define B200FP8_DEV_OK 0u
@@ -225,6 +227,16 @@ int b200fp8_peer_barrier(uint32_t* const* flag_arrays, int n, int rank, uint32_t
                          uint32_t* status_word, void* stream);
 
 /*
+ * The same barrier with the caller's own bound on the wait, in SM clocks (>= 1): for callers that
+ * know their ranks are in step and want a lost peer reported within milliseconds, and for testing
+ * the time-out path without a peer (n = 2 with both flag arrays local and the second slot never
+ * published: the kernel returns after `limit_clocks` with B200FP8_DEV_WAIT_TIMEOUT in the status
+ * word; nothing faults). No counterpart in the reference.
+ */
+int b200fp8_peer_barrier_limited(uint32_t* const* flag_arrays, int n, int rank, uint32_t epoch,
+                                 int64_t limit_clocks, uint32_t* status_word, void* stream);
+
+/*
  * CUDA IPC helpers for b200fp8_gemm_scatter (no counterpart in the reference). export: a
  * 64-byte handle of the device allocation that contains ptr, and ptr's byte offset inside it;
  * the handle travels to the other process by any host channel. open: maps that allocation
@@ -240,6 +252,14 @@ int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int varian
 
 /* The variant B200FP8_VARIANT_AUTO resolves to for this shape on the current device. */
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K);
+
+/*
+ * How many CTA pairs (clusters of two, one CTA per SM) of the B200FP8_VARIANT_PAIR256* kernels the
+ * current device can hold at once: the persistent grid of those kernels. 0 = the device cannot run
+ * them. (The reference's counterpart is the `num_sm_multiplier` / persistent-grid choice inside its
+ * tuned Helion configs, torch-ext/finegrained_fp8_helion/_helion_aot_fp8_cuda_sm100.py:13-28.)
+ */
+int b200fp8_gemm_pair_clusters(void);
 
 /*
  * Decode-shape GEMM for callers that must not allocate device memory. No counterpart in the

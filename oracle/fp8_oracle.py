@@ -2,8 +2,10 @@
 
 This file restates, on the CPU with plain torch / numpy, the arithmetic of the
 reference package ``finegrained-fp8-helion`` (AmesingFlank/hf_kernels_helion).
-Only ``tests/``, ``__graft_entry__.smoke()`` and the ``cpu_baseline`` / ``--impl
-reference`` legs of ``bench.py`` may import it; the product package never does.
+Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py`` may import it - ``bench.py`` in two
+places: the ``cpu_baseline`` / ``--impl reference`` legs (where it is the timed CPU baseline) and the
+parity check after the timed regions (where it checks sampled rows of the GPU result); the
+product package never does.
 
 What each function follows (paths are relative to the reference repository):
 

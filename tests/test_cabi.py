@@ -159,3 +159,47 @@ def test_streamk_partition_covers_every_unit_once(lib, tiles, num_kb, grid):
             first_tile_of_c = first[c] // num_kb
             read[(t, c)] = 2 * c + (0 if first_tile_of_c == t else 1)
     assert read == written
+
+
+@pytest.mark.gpu
+def test_peer_barrier_wait_runs_out_cleanly(lib, device):
+    """A bounded device-side wait that really runs out, without a fault or a hang: the barrier kernel
+    is told there are two GPUs, both flag arrays are this GPU's own, and nobody ever publishes the
+    second slot. After `limit_clocks` (about a millisecond) the kernel records
+    B200FP8_DEV_WAIT_TIMEOUT in the status word and returns; the host raises; the device stays usable."""
+    import time
+
+    import torch
+
+    from hf_kernels_helion_b200 import _lib, runtime
+    from oracle import fp8_oracle as oracle
+
+    runtime.check_device_status(device)                       # start clean
+    flags = torch.zeros(8, dtype=torch.int32, device=device)
+    arr = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr())
+    word = runtime.status_word(device)
+    stream = torch.cuda.current_stream(device).cuda_stream
+    t0 = time.perf_counter()
+    with torch.cuda.device(device):
+        st = lib.b200fp8_peer_barrier_limited(arr, 2, 0, 1, 2_000_000, word.data_ptr(), stream)
+    assert st == 0
+    torch.cuda.synchronize(device)
+    assert time.perf_counter() - t0 < 1.0                      # 2e6 clocks is about a millisecond
+    assert int(word.item()) == 1                               # B200FP8_DEV_WAIT_TIMEOUT
+    assert int(flags[0].item()) == 1 and int(flags[1].item()) == 0    # own epoch published, peer slot untouched
+    with pytest.raises(RuntimeError, match="device status 1"):
+        runtime.check_device_status(device)
+    runtime.check_device_status(device)                       # the check cleared the word
+    # a barrier whose peers have all published returns at once and leaves the word clean
+    flags[1] = 2
+    with torch.cuda.device(device):
+        assert lib.b200fp8_peer_barrier_limited(arr, 2, 0, 2, 2_000_000, word.data_ptr(), stream) == 0
+    runtime.check_device_status(device)
+    # argument errors
+    assert lib.b200fp8_peer_barrier_limited(arr, 2, 0, 1, 0, word.data_ptr(), stream) == 2
+    assert lib.b200fp8_peer_barrier_limited(None, 2, 0, 1, 1000, word.data_ptr(), stream) == 1
+    # and the device still computes
+    A, B, As, Bs = oracle.make_quantised_inputs(130, 256, 256, 5)
+    out = runtime.gemm(A.to(device), B.to(device), As.to(device), Bs.to(device), 128, 128, torch.float32)
+    runtime.check_device_status(device)
+    assert oracle.max_err_over_rms(out.cpu(), oracle.gemm_dequant(A, B, As, Bs)) <= 1e-4

@@ -25,7 +25,7 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 FP32_TOL = 1e-4
-VARIANTS_BIG = ["tile128", "tile256"]
+VARIANTS_BIG = ["tile128", "tile256", "pair256", "pair256_split"]
 
 
 def _dev(ts, device):
@@ -38,7 +38,7 @@ def _run(device, A, B, As, Bs, dtype, variant):
     return out.cpu()
 
 
-@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk", "auto"])
+@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk", "pair256", "pair256_split", "auto"])
 @pytest.mark.parametrize("name", ["small_96x256x384", "small_130x128x256", "small_1x384x512"])
 def test_golden_vectors_from_reference_source(device, name, variant):
     z = np.load(GOLDEN / f"{name}.npz")

@@ -43,6 +43,53 @@ def test_act_quant_value_ranges(device):
     assert not torch.isnan(q.float()).any()
 
 
+def _assert_same_with_nans(q, s, q_ref, s_ref):
+    """Bytes and scales as the checker's, where a NaN byte may differ in its sign bit (the sign of an
+    inf / inf or x / NaN quotient is the platform's choice) and a NaN scale in its payload."""
+    qb, qr = q.cpu().view(torch.uint8), q_ref.view(torch.uint8)
+    nan_b, nan_r = (qb & 0x7F) == 0x7F, (qr & 0x7F) == 0x7F
+    assert torch.equal(nan_b, nan_r)
+    assert torch.equal(qb[~nan_b], qr[~nan_r])
+    sc, sr = s.cpu(), s_ref
+    assert torch.equal(torch.isnan(sc), torch.isnan(sr))
+    keep = ~torch.isnan(sr)
+    assert torch.equal(sc[keep].view(torch.int32), sr[keep].view(torch.int32))
+
+
+@pytest.mark.parametrize("K", [512, 200])        # the contiguous kernel and the strided / ragged one
+def test_act_quant_nan_and_inf_groups(device, K):
+    """A NaN anywhere in a group reaches the group's scale (scale NaN, every byte of the group NaN);
+    an Inf makes the scale infinite: finite elements become zero, infinite ones NaN. Other groups of
+    the same row are untouched."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(8, K, generator=g)
+    x[0, 5] = float("nan")
+    x[1, 130] = float("nan")
+    x[1, 131] = float("inf")
+    x[2, 0] = float("inf")
+    x[3, 127] = float("-inf")
+    x[3, 3] = float("inf")
+    x[4, K - 1] = float("nan")
+    x = x.to(torch.bfloat16)
+    q_ref, s_ref = oracle.quant_act(x)
+    assert torch.isnan(s_ref[0, 0]) and torch.isinf(s_ref[2, 0])           # the checker propagates them
+    q, s = pkg.fp8_act_quant(x.to(device))
+    _assert_same_with_nans(q, s, q_ref, s_ref)
+    assert (q.cpu().view(torch.uint8)[0, :128] & 0x7F).eq(0x7F).all()        # whole group NaN
+    assert not torch.isnan(s.cpu()[0, 1:]).any()
+
+
+def test_weight_quant_nan_block(device):
+    g = torch.Generator().manual_seed(12)
+    w = (torch.randn(256, 384, generator=g) * 0.02)
+    w[130, 7] = float("nan")
+    w[5, 300] = float("inf")
+    w = w.to(torch.bfloat16)
+    q_ref, s_ref = oracle.quant_weight(w)
+    q, s = pkg.fp8_weight_quant(w.to(device))
+    _assert_same_with_nans(q, s, q_ref, s_ref)
+
+
 def test_act_quant_every_bf16_value(device):
     """All 65536 bf16 bit patterns that are finite, paired with several group maxima."""
     bits = torch.arange(0, 65536, dtype=torch.int32).to(torch.int16)

@@ -55,6 +55,9 @@ def _worker(rank, world, port, q):
             ok = ok and torch.equal(got32, ref32)
             runtime.check_device_status()
         q.put((rank, (bool(ok), used_mc)))
+        # no rank may tear down its IPC / multicast mappings while a peer's kernels still use them
+        torch.cuda.synchronize()
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
@@ -69,9 +72,23 @@ def test_sharded_linear_nccl():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
-    res = dict(q.get(timeout=5) for _ in range(world))
+    res = {}
+    try:
+        for _ in range(world):
+            rank, val = q.get(timeout=300)
+            res[rank] = val
+        for p in procs:
+            p.join(60)
+    finally:
+        # a worker that hangs (rendezvous, IPC open, a peer that died) must not outlive the test with
+        # its GPU memory and kernels: end it by its own handle
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(5)
+    assert [p.exitcode for p in procs] == [0] * world
     assert {r: v[0] for r, v in res.items()} == {r: True for r in range(world)}
     print("multimem exchange exercised:", all(v[1] for v in res.values()))
