@@ -406,6 +406,11 @@ def main_ours(args):
     # ---- the same steps for at least two seconds, device-timed: the rate the part sustains under its
     #      power limit, with the clocks sampled over exactly this region
     sus_iters = max(10, int(2200.0 / max(ms_total / steps, 1e-3)) + 1)
+    if world > 1:
+        # every rank must run the same number of steps (they meet in a barrier every step)
+        n_it = torch.tensor([sus_iters], dtype=torch.int64, device=dev)
+        dist.broadcast(n_it, src=0)
+        sus_iters = int(n_it.item())
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ts0 = time.time()

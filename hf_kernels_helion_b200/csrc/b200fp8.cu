@@ -56,20 +56,20 @@ int device_info(const DeviceInfo** out) {
         cudaFuncAttributes attr;
         ok = ok && cudaFuncGetAttributes(&attr, fn) == cudaSuccess && attr.numRegs * threads >= regs_needed_total;
       };
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256>::THREADS,
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, 0>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_streamk_kernel<256>), StreamKCfg<256>::THREADS,
               128 * StreamKCfg<256>::REGS_CONTROL + 256 * StreamKCfg<256>::REGS_EPILOGUE);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false>), TileCfg<128, false>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, false>), TileCfg<256, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<128, 0>), TileCfg<128, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, 0>), TileCfg<256, false>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128, false>::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128>::THREADS,
               128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<128, false>), TileCfg<128>::THREADS,
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<128, 0>), TileCfg<128>::THREADS,
               128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128>::THREADS,
               128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
@@ -85,8 +85,8 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_tile_decode_kernel<256, 64>), TileCfg<256, false, 64>::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_decode_kernel<256, 64>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256, false>::SMEM_BYTES);
-      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, true>), TileCfg<256>::THREADS,
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, 1>), TileCfg<256, false>::SMEM_BYTES);
+      regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<256, 1>), TileCfg<256>::THREADS,
               128 * TileCfg<256>::REGS_CONTROL + 256 * TileCfg<256>::REGS_EPILOGUE);
       using PairCfg = TileCfg<256, false, 128, 1>;
       using PairMultiCfg = TileCfg<256, true, 128, 1>;
@@ -337,7 +337,7 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
     err = cudaLaunchKernelEx(&cfg, gemm_tile_decode_kernel<256, 64>, ta, tb, args);
   } else if (BN == 256 && args.sk_split >= 2) {
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, true>, ta, tb, args);
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, 1>, ta, tb, args);
   } else if (BN == 128 && args.BsT != nullptr) {
     cfg.dynamicSmemBytes = TileCfg<128, false>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_rowb_kernel<128>, ta, tb, args);
@@ -357,7 +357,7 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
     err = cudaLaunchKernelEx(&cfg, gemm_tile_multi_kernel<BN>, ta, tb, args, dm);
   } else {
     cfg.dynamicSmemBytes = TileCfg<BN, false>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, false>, ta, tb, args);
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<BN, 0>, ta, tb, args);
   }
   if (err != cudaSuccess) {
     cudaGetLastError();

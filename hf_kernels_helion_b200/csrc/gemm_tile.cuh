@@ -38,8 +38,8 @@ struct GemmArgs {
   // round-robin as whole tiles; the remaining R < grid tiles - the last, partly empty wave -
   // are each cut into sk_split K ranges of sk_kb_per K blocks, one range per CTA, so that the
   // tail takes 1 / sk_split of a tile time. CTA c < R * sk_split works on tile sk_full + c /
-  // sk_split, range c % sk_split, and leaves its fp32 partial sums in `partial` as
-  // [c][128][BN]; tile_sk_fixup_kernel adds the ranges of each tail tile in a fixed order.
+  // sk_split, range c % sk_split, and leaves its fp32 partial sums in slot c of `partial` (layout:
+  // sk_partial_ptr); tile_sk_fixup_kernel adds the ranges of each tail tile in a fixed order.
   int sk_full, sk_split, sk_kb_per;
   float* partial;
   // Destinations of the result: dst[0] is C itself; dst[1..n_dst-1] are further buffers that
@@ -151,9 +151,20 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   m_blk = m_first + (rem - n_blk * gm);
 }
 
+// Partial tiles in the workspace (split-K forms): per slot a [BN / 4][128] array of float4, i.e.
+// groups of four columns outermost and the tile's rows innermost, so that the 32 lanes of a warp -
+// which own consecutive rows - write and read 512 contiguous bytes per instruction (a row-major
+// tile costs 32 separate 16-byte transactions per instruction and was measured at ~8 us per 128 KiB
+// tile and direction).
+template <int BN>
+__device__ __forceinline__ float4* sk_partial_ptr(float* partial, int slot, int col4, int row) {
+  return reinterpret_cast<float4*>(partial) + (static_cast<int64_t>(slot) * (BN / 4) + col4) * 128 + row;
+}
+
 // One CTA's work as a sequence of segments = (output tile, K-block range).
 struct Segment {
   int m_blk, n_blk, kb_begin, kb_end;
+  int tile;     // index of the tile in raster order
   bool first;   // first segment of this CTA
 };
 
@@ -165,7 +176,7 @@ struct SegCursor {
   bool started;
 };
 
-template <bool SK>
+template <int SK>
 __device__ __forceinline__ SegCursor seg_begin(int worker, int nworkers) {
   SegCursor c;
   c.tile = worker;
@@ -191,34 +202,35 @@ __device__ __forceinline__ bool seg_tail(const GemmArgs& a, int worker, int num_
 }
 
 // Number of K blocks this CTA processes in total.
-template <bool SK>
+template <int SK>
 __device__ __forceinline__ uint32_t seg_total_kblocks(const GemmArgs& a, int worker, int nworkers, int num_m, int num_n,
                                                       int num_kb, int num_tiles) {
   const int whole_end = SK ? a.sk_full : num_tiles;
   int mine = 0;
   if (worker < whole_end) mine = (whole_end - worker + nworkers - 1) / nworkers;
   uint32_t total = static_cast<uint32_t>(mine) * static_cast<uint32_t>(num_kb);
-  if constexpr (SK) {
+  if constexpr (SK == 1) {
     Segment s;
     if (seg_tail(a, worker, num_m, num_n, num_kb, num_tiles, s)) total += static_cast<uint32_t>(s.kb_end - s.kb_begin);
   }
   return total;
 }
 
-template <bool SK>
+template <int SK>
 __device__ __forceinline__ bool seg_next(SegCursor& c, const GemmArgs& a, int num_m, int num_n, int num_kb, int num_tiles,
                                          Segment& s) {
   s.first = !c.started;
-  c.started = true;
   const int whole_end = SK ? a.sk_full : num_tiles;
+  c.started = true;
   if (c.tile < whole_end) {
+    s.tile = c.tile;
     tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
     s.kb_begin = 0;
     s.kb_end = num_kb;
     c.tile += c.nworkers;
     return true;
   }
-  if constexpr (SK) {
+  if constexpr (SK == 1) {
     if (!c.tail_done) {
       c.tail_done = true;
       return seg_tail(a, c.worker, num_m, num_n, num_kb, num_tiles, s);
@@ -237,7 +249,7 @@ struct DstMaps {
 // multimem.st to a multicast address, otherwise by TMA stores to up to eight destinations.
 // ROWB: B carries one scale per ROW and K block (the deep-gemm layout) instead of one per
 // 128 x 128 block: the promotion multiplies every accumulator column by its own scale.
-template <int BN, bool MULTI, bool SK, bool MC = false, bool ROWB = false, int A_ROWS = 128, int PAIR = 0>
+template <int BN, bool MULTI, int SK, bool MC = false, bool ROWB = false, int A_ROWS = 128, int PAIR = 0>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmArgs& args, const CUtensorMap* dmaps) {
   using Cfg = TileCfg<BN, MULTI, A_ROWS, PAIR>;
@@ -620,11 +632,10 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         // tail split-K: this CTA saw only part of the K range - leave the fp32 partial sums of the
         // rows that exist in the workspace; tile_sk_fixup_kernel adds the ranges of the tile
         if (row < M) {
-          const int64_t slot = static_cast<int64_t>(blockIdx.x);
-          float* prow = args.partial + (slot * Cfg::BM + (q * 32 + lane)) * BN + cw * Cfg::EPI_COLS;
+          float4* pcol = sk_partial_ptr<BN>(args.partial, static_cast<int>(blockIdx.x), cw * (Cfg::EPI_COLS / 4), q * 32 + lane);
 #pragma unroll
           for (int j = 0; j < Cfg::EPI_COLS; j += 4)
-            *reinterpret_cast<float4*>(prow + j) = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
+            pcol[(j / 4) * Cfg::BM] = make_float4(ACC(j), ACC(j + 1), ACC(j + 2), ACC(j + 3));
         }
       } else if (MULTI && (MC || args.staged_store)) {
         // Multi-destination and multicast forms: per pass, 128 bytes of each of this warp's 32 rows
@@ -768,7 +779,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   }
 }
 
-template <int BN, bool SK>
+template <int BN, int SK>
 __global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
 gemm_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs args) {
@@ -781,14 +792,14 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(TileCfg<256, false>::THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs args) {
-  gemm_tile_body<256, false, false, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, nullptr);
+  gemm_tile_body<256, false, 0, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, nullptr);
 }
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(TileCfg<256, true>::THREADS, 1)
 gemm_pair_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
-  gemm_tile_body<256, true, false, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, dmaps.m);
+  gemm_tile_body<256, true, 0, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, dmaps.m);
 }
 
 // Multi-destination form: the finished tile is staged in shared memory and sent to every
@@ -797,7 +808,7 @@ template <int BN>
 __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
-  gemm_tile_body<BN, true, false>(tmap_a, tmap_b, args, dmaps.m);
+  gemm_tile_body<BN, true, 0>(tmap_a, tmap_b, args, dmaps.m);
 }
 
 // Decode forms: 16-row A slots and six pipeline stages (M <= 16), 64-row slots and five (M <= 64).
@@ -805,7 +816,7 @@ template <int BN, int A_ROWS>
 __global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
 gemm_tile_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmArgs args) {
-  gemm_tile_body<BN, false, false, false, false, A_ROWS>(tmap_a, tmap_b, args, nullptr);
+  gemm_tile_body<BN, false, 0, false, false, A_ROWS>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Row-scaled B (deep-gemm layout): single destination, 128-wide tiles.
@@ -813,7 +824,7 @@ template <int BN>
 __global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
 gemm_tile_rowb_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmArgs args) {
-  gemm_tile_body<BN, false, false, false, true>(tmap_a, tmap_b, args, nullptr);
+  gemm_tile_body<BN, false, 0, false, true>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Multicast form: args.dst[0] is a multimem address; every 128-byte row segment of a finished
@@ -822,7 +833,7 @@ template <int BN>
 __global__ void __launch_bounds__(TileCfg<BN, true>::THREADS, 1)
 gemm_tile_mc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs args) {
-  gemm_tile_body<BN, true, false, true>(tmap_a, tmap_b, args, nullptr);
+  gemm_tile_body<BN, true, 0, true>(tmap_a, tmap_b, args, nullptr);
 }
 
 // Prep kernel of b200fp8_linear: quantises the bf16 activations (same arithmetic as
@@ -877,10 +888,11 @@ tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int6
   for (int j = 0; j < sk_split; ++j) {
     if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
     const int64_t slot = static_cast<int64_t>(blockIdx.x) * sk_split + j;
-    const float* src = partial + (slot * 128 + r0) * BN + threadIdx.x;
+    // element (row, column c) of a slot sits at float index ((c / 4) * 128 + row) * 4 + c % 4
+    const float* src = partial + ((slot * (BN / 4) + (threadIdx.x >> 2)) * 128 + r0) * 4 + (threadIdx.x & 3);
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      if (static_cast<int64_t>(m_blk) * 128 + r0 + i < M) sum[i] += __ldg(src + static_cast<int64_t>(i) * BN);
+      if (static_cast<int64_t>(m_blk) * 128 + r0 + i < M) sum[i] += __ldg(src + i * 4);
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
