@@ -162,7 +162,33 @@ EncodeTiledFn encode_fn() {
 
 // 2-D tensor map over a row-major byte matrix [rows, cols] with row stride ld (bytes),
 // box = [box_rows x 128 bytes], 128-byte swizzle, zero fill outside the matrix.
+// A tensor map is a pure function of (base, rows, cols, ld, box_rows): the last few are kept per
+// host thread (no lock, no shared mutable state) so that a caller that repeats a shape - a decode
+// loop, a captured graph being re-recorded - does not pay the driver's encoder on every call.
+struct TmapKey {
+  const void* base;
+  int64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+constexpr int kTmapCacheEntries = 16;
+struct TmapCache {
+  TmapKey key[kTmapCacheEntries];
+  CUtensorMap map[kTmapCacheEntries];
+  int used = 0, next = 0;
+};
+thread_local TmapCache t_tmap_cache;
+
 int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_rows) {
+  const TmapKey k = {base, rows, cols, ld, box_rows};
+  TmapCache& c = t_tmap_cache;
+  for (int i = 0; i < c.used; ++i)
+    if (c.key[i] == k) {
+      *map = c.map[i];
+      return B200FP8_OK;
+    }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return B200FP8_ERR_DRIVER;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -172,7 +198,12 @@ int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200FP8_OK : B200FP8_ERR_DRIVER;
+  if (r != CUDA_SUCCESS) return B200FP8_ERR_DRIVER;
+  const int slot = c.used < kTmapCacheEntries ? c.used++ : c.next;
+  c.next = (slot + 1) % kTmapCacheEntries;
+  c.key[slot] = k;
+  c.map[slot] = *map;
+  return B200FP8_OK;
 }
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200FP8_OK : B200FP8_ERR_LAUNCH; }

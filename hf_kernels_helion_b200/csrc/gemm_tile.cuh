@@ -279,6 +279,10 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   const bool leader = cta_rank == 0u;
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int nworkers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  // With a single block of rows and fewer than 97 of them (decode shapes) the upper TMEM lane
+  // quarters hold rows that do not exist: the promotion warps of those quarters have nothing to
+  // do and sit the kernel out (fewer instructions issued, and fewer arrivals per TMEM stage).
+  const int live_quarters = (!PAIR && args.M <= 96) ? static_cast<int>((args.M + 31) / 32) : 4;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -287,7 +291,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     }
     for (uint32_t s = 0; s < TS * H; ++s) {
       mbar_init(&tfull[s], 1);
-      mbar_init(&tempty[s], (Cfg::EPI_WARPS / H) * (PAIR ? 2 : 1));
+      mbar_init(&tempty[s], PAIR ? 2 * (Cfg::EPI_WARPS / H) : (Cfg::EPI_WARPS / 4) * live_quarters);
     }
     *abort_flag = 0u;
     fence_barrier_init();
@@ -325,7 +329,12 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
-      if (args.a_from_prep) asm volatile("griddepcontrol.wait;" ::: "memory");
+      // When A comes from the prep kernel of the same call (which may still be running: programmatic
+      // dependent launch), the weight loads of the first K blocks do not wait for it: they are issued
+      // at once, the A loads of those stages follow after griddepcontrol.wait.
+      bool a_pending = args.a_from_prep != 0;
+      uint32_t pend_from = 0;
+      int pend_kb0 = 0, pend_m0 = 0;
       const uint64_t pol_stream = policy_evict_first();
       const uint64_t pol_keep = policy_evict_last();
       uint32_t it = 0;
@@ -360,13 +369,27 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
             continue;
           }
           mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          if (A_ROWS < 128 || num_m == 1) {
-            // one M block: the weight is read exactly once, the few activation rows by every CTA
-            tma_load_2d_hint(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0, pol_keep);
-            tma_load_2d_hint(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0, pol_stream);
+          // one M block: the weight is read exactly once, the few activation rows by every CTA
+          const bool hinted = A_ROWS < 128 || num_m == 1;
+          auto load_a = [&](uint32_t stage, int kb_a, int m0_a) {
+            uint8_t* dst = smem + stage * Cfg::STAGE_BYTES;
+            if (hinted) tma_load_2d_hint(dst, &tmap_a, &full[stage], kb_a * Cfg::BK, m0_a, pol_keep);
+            else tma_load_2d(dst, &tmap_a, &full[stage], kb_a * Cfg::BK, m0_a);
+          };
+          if (hinted) tma_load_2d_hint(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0, pol_stream);
+          else tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+          if (!a_pending) {
+            load_a(s, kb, m0);
           } else {
-            tma_load_2d(a_dst, &tmap_a, &full[s], kb * Cfg::BK, m0);
-            tma_load_2d(b_dst, &tmap_b, &full[s], kb * Cfg::BK, n0);
+            if (it == pend_from) {
+              pend_kb0 = kb;
+              pend_m0 = m0;
+            }
+            if (it + 1 - pend_from == static_cast<uint32_t>(STAGES) || kb + 1 == seg.kb_end) {
+              asm volatile("griddepcontrol.wait;" ::: "memory");
+              a_pending = false;
+              for (uint32_t j = pend_from; j <= it; ++j) load_a(j % STAGES, pend_kb0 + static_cast<int>(j - pend_from), pend_m0);
+            }
           }
         }
       }
@@ -461,6 +484,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ promotion + epilogue
+    // (setmaxnreg is a warpgroup-wide instruction: the warps that sit out execute it too)
     if constexpr (Cfg::REBALANCE_REGS) setmaxnreg_inc<Cfg::REGS_EPILOGUE>();
     const int e = warp - 4;
     const int q = warp & 3;           // TMEM lane quarter this warp may read
@@ -469,7 +493,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     constexpr int CHUNKS = Cfg::EPI_COLS / 32;
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
-    bool ok = true;
+    bool ok = (warp & 3) < live_quarters;
     // the scale copy AsT is written by the preceding tile_prep_kernel; with programmatic
     // dependent launch this kernel may have started before that grid finished
     asm volatile("griddepcontrol.wait;" ::: "memory");
