@@ -66,7 +66,7 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_tile_kernel<256, 0>), TileCfg<256, false>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<128>), TileCfg<128, true>::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_tile_multi_kernel<256>), TileCfg<256, true>::SMEM_BYTES);
-      opt_in(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128, false>::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128, false>::SMEM_BYTES + kRowbTableBytes);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_rowb_kernel<128>), TileCfg<128>::THREADS,
               128 * TileCfg<128>::REGS_CONTROL + 256 * TileCfg<128>::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_tile_kernel<128, 0>), TileCfg<128>::THREADS,
@@ -169,8 +169,9 @@ struct TmapKey {
   const void* base;
   int64_t rows, cols, ld;
   uint32_t box_rows;
+  int kind;   // 0: byte matrix, 128-byte boxes, SWIZZLE_128B; 1: fp32 matrix, 128-element boxes, no swizzle
   bool operator==(const TmapKey& o) const {
-    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && kind == o.kind;
   }
 };
 constexpr int kTmapCacheEntries = 16;
@@ -181,8 +182,9 @@ struct TmapCache {
 };
 thread_local TmapCache t_tmap_cache;
 
-int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_rows) {
-  const TmapKey k = {base, rows, cols, ld, box_rows};
+// kind 0: byte matrix [rows, cols], ld in bytes; kind 1: fp32 matrix [rows, cols], ld in bytes, box = [box_rows x 128 floats]
+int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_rows, int kind) {
+  const TmapKey k = {base, rows, cols, ld, box_rows, kind};
   TmapCache& c = t_tmap_cache;
   for (int i = 0; i < c.used; ++i)
     if (c.key[i] == k) {
@@ -195,15 +197,20 @@ int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
   const cuuint32_t box[2] = {128u, box_rows};
   const cuuint32_t elem[2] = {1u, 1u};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = fn(map, kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                        const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return B200FP8_ERR_DRIVER;
   const int slot = c.used < kTmapCacheEntries ? c.used++ : c.next;
   c.next = (slot + 1) % kTmapCacheEntries;
   c.key[slot] = k;
   c.map[slot] = *map;
   return B200FP8_OK;
+}
+
+int make_tmap_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_rows) {
+  return make_tmap(map, base, rows, cols, ld, box_rows, 0);
 }
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200FP8_OK : B200FP8_ERR_LAUNCH; }
@@ -370,8 +377,15 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
     cfg.dynamicSmemBytes = TileCfg<256, false>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_kernel<256, 1>, ta, tb, args);
   } else if (BN == 128 && args.BsT != nullptr) {
-    cfg.dynamicSmemBytes = TileCfg<128, false>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_tile_rowb_kernel<128>, ta, tb, args);
+    // the K-block-major copy of the row scales as an fp32 matrix [K blocks, n_pad]: one box = the
+    // table of one tile (used when it fits the shared-memory table)
+    CUtensorMap tbst;
+    const int64_t kblocks = (args.K + 127) / 128;
+    st = make_tmap(&tbst, args.BsT, kblocks, args.n_pad, args.n_pad * 4,
+                   static_cast<uint32_t>(kblocks < kRowbTableKb ? kblocks : kRowbTableKb), 1);
+    if (st != B200FP8_OK) return st;
+    cfg.dynamicSmemBytes = TileCfg<128, false>::SMEM_BYTES + kRowbTableBytes;
+    err = cudaLaunchKernelEx(&cfg, gemm_tile_rowb_kernel<128>, ta, tb, tbst, args);
   } else if (args.mc_store) {
     cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_mc_kernel<BN>, ta, tb, args);
@@ -692,6 +706,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
       if (st != B200FP8_OK) return st;
     }
     args.BsT = nullptr;
+    args.rowb_table = 0;
     args.n_pad = align_up(N, 128);
     if (fq.rowb) {
       // second transposition: the row scales of B, K-block-major (same kernel, B in the role of A)
@@ -702,6 +717,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
       st = launch_status();
       if (st != B200FP8_OK) return st;
       args.BsT = bst;
+      args.rowb_table = kblocks <= kRowbTableKb ? 1 : 0;
     }
     args.As = As;
     args.Bs = Bs;
@@ -719,9 +735,9 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
     if (sk) {
       st = launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream, skp.grid);
       if (st != B200FP8_OK) return st;
-      const dim3 fix_grid(static_cast<unsigned>(skp.tail), 16u);
+      const dim3 fix_grid(static_cast<unsigned>(skp.tail), 4u);
       tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, skp.num_kb, ldc,
-                                                         out_dtype == B200FP8_OUT_FP32, 256, skp.num_m, skp.num_n,
+                                                         out_dtype == B200FP8_OUT_FP32, skp.num_m, skp.num_n,
                                                          skp.full, skp.split, skp.kb_per);
       return launch_status();
     }

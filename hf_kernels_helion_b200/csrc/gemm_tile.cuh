@@ -63,6 +63,10 @@ struct GemmArgs {
   // (n_pad = N rounded up to 128, padding zero); Bs / ld_bs are then unused by the GEMM kernel.
   const float* BsT;
   int64_t n_pad;
+  // 1: the row-scaled kernel keeps the B scales of the current tile ([K blocks][128 columns]) in shared
+  // memory, loaded by the producer with one TMA box per tile (K <= kRowbTableKb * 128); 0: it reads them
+  // from BsT in global memory on every K block.
+  int rowb_table;
   const float* As;
   const float* Bs;
   void* C;
@@ -141,12 +145,17 @@ struct TileCfg {
 // A rows and B rows they share are fetched from DRAM once and hit in L2 afterwards.
 constexpr int kRasterGroup = 32;
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-  const int per_panel = kRasterGroup * num_n;
+// Row-scaled kernel: K blocks of per-column B scales held in shared memory per tile (128 floats each).
+constexpr int kRowbTableKb = 64;
+constexpr int kRowbTableBytes = kRowbTableKb * 128 * 4;
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk,
+                                            int group = kRasterGroup) {
+  const int per_panel = group * num_n;
   const int panel = tile / per_panel;
   const int rem = tile - panel * per_panel;
-  const int m_first = panel * kRasterGroup;
-  const int gm = (num_m - m_first) < kRasterGroup ? (num_m - m_first) : kRasterGroup;
+  const int m_first = panel * group;
+  const int gm = (num_m - m_first) < group ? (num_m - m_first) : group;
   n_blk = rem / gm;
   m_blk = m_first + (rem - n_blk * gm);
 }
@@ -172,6 +181,7 @@ struct Segment {
 struct SegCursor {
   int tile;          // next whole tile of the round-robin part
   int worker, nworkers;
+  int group;         // row blocks per panel of the tile order
   bool tail_done;    // the tail range of this worker (SK kernels) has been handed out
   bool started;
 };
@@ -182,6 +192,7 @@ __device__ __forceinline__ SegCursor seg_begin(int worker, int nworkers) {
   c.tile = worker;
   c.worker = worker;
   c.nworkers = nworkers;
+  c.group = kRasterGroup;
   c.tail_done = false;
   c.started = false;
   return c;
@@ -224,7 +235,7 @@ __device__ __forceinline__ bool seg_next(SegCursor& c, const GemmArgs& a, int nu
   c.started = true;
   if (c.tile < whole_end) {
     s.tile = c.tile;
-    tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk);
+    tile_coords(c.tile, num_m, num_n, s.m_blk, s.n_blk, c.group);
     s.kb_begin = 0;
     s.kb_end = num_kb;
     c.tile += c.nworkers;
@@ -251,7 +262,8 @@ struct DstMaps {
 // 128 x 128 block: the promotion multiplies every accumulator column by its own scale.
 template <int BN, bool MULTI, int SK, bool MC = false, bool ROWB = false, int A_ROWS = 128, int PAIR = 0>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
-                                               const GemmArgs& args, const CUtensorMap* dmaps) {
+                                               const GemmArgs& args, const CUtensorMap* dmaps,
+                                               const CUtensorMap* tmap_bst = nullptr) {
   using Cfg = TileCfg<BN, MULTI, A_ROWS, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
@@ -261,13 +273,17 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* out_stage = smem + STAGES * Cfg::STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::OUT_STAGE_BYTES);
+  static_assert(!(ROWB && MULTI), "the row-scaled kernel has one destination");
+  float* rowb_table = reinterpret_cast<float*>(out_stage);   // ROWB: [kRowbTableKb][128] B scales of the current tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + (ROWB ? kRowbTableBytes : Cfg::OUT_STAGE_BYTES));
   uint64_t* full = bars;                  // [STAGES]  TMA bytes landed
   uint64_t* empty = bars + STAGES;        // [STAGES]  MMA finished reading the slot
   uint64_t* tfull = bars + 2 * STAGES;    // [TS * H]  TMEM stage (half) holds a finished K-block partial
   uint64_t* tempty = bars + 2 * STAGES + TS * H;  // [TS * H]  every epilogue warp has read the TMEM stage (half)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * TS * H);
-  static_assert((2 * STAGES + 2 * TS * H) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
+  uint64_t* sfull = bars + 2 * STAGES + 2 * TS * H;     // ROWB: the tile's scale table has landed
+  uint64_t* sempty = sfull + 1;                           // ROWB: every promotion warp is done with the table
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * TS * H + 2);
+  static_assert((2 * STAGES + 2 * TS * H + 2) * 8 + 8 <= Cfg::BAR_BYTES, "barrier area too small");
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -293,6 +309,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       mbar_init(&tfull[s], 1);
       mbar_init(&tempty[s], PAIR ? 2 * (Cfg::EPI_WARPS / H) : (Cfg::EPI_WARPS / 4) * live_quarters);
     }
+    mbar_init(sfull, 1);
+    mbar_init(sempty, (Cfg::EPI_WARPS / 4) * live_quarters);
     *abort_flag = 0u;
     fence_barrier_init();
   }
@@ -333,6 +351,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       // dependent launch), the weight loads of the first K blocks do not wait for it: they are issued
       // at once, the A loads of those stages follow after griddepcontrol.wait.
       bool a_pending = args.a_from_prep != 0;
+      uint32_t tile_no = 0;
+      (void)tile_no;
       uint32_t pend_from = 0;
       int pend_kb0 = 0, pend_m0 = 0;
       const uint64_t pol_stream = policy_evict_first();
@@ -340,11 +360,23 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       uint32_t it = 0;
       bool ok = true;
       SegCursor cur = seg_begin<SK>(worker, nworkers);
+      if constexpr (PAIR) cur.group = kRasterGroup / 2;   // 256-row tiles: the same 4096 rows per panel
       Segment seg;
       const uint32_t full_leader = PAIR ? mapa_shared(smem_u32(full), 0u) : 0u;
       while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
         const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
         const int n0 = seg.n_blk * BN;
+        if constexpr (ROWB) {
+          if (args.rowb_table) {
+            // the B scales of this tile: one box [K blocks x 128 columns] of the K-block-major copy, once
+            // the promotion warps have let go of the previous tile's table
+            if (!mbar_wait(sempty, (tile_no & 1u) ^ 1u, abort_flag, status_word)) { ok = false; break; }
+            if (tile_no == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // the copy is written by the prep launch
+            mbar_arrive_expect_tx(sfull, static_cast<uint32_t>(num_kb) * 512u);
+            tma_load_2d(rowb_table, tmap_bst, sfull, n0, 0);
+            ++tile_no;
+          }
+        }
         for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -493,6 +525,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     constexpr int CHUNKS = Cfg::EPI_COLS / 32;
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
+    uint32_t rowb_tile = 0;
+    (void)rowb_tile;
     bool ok = (warp & 3) < live_quarters;
     // the scale copy AsT is written by the preceding tile_prep_kernel; with programmatic
     // dependent launch this kernel may have started before that grid finished
@@ -509,6 +543,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       }
     };
     SegCursor cur = seg_begin<SK>(worker, nworkers);
+      if constexpr (PAIR) cur.group = kRasterGroup / 2;   // 256-row tiles: the same 4096 rows per panel
     Segment seg;
     while (ok && seg_next<SK>(cur, args, num_m, num_n, num_kb, num_tiles, seg)) {
       const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BM;
@@ -533,11 +568,16 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       // block, the same for all lanes of the warp. They are fetched (16 broadcast loads of 16
       // bytes from the K-block-major copy) before the wait for the MMA, so that they arrive
       // while the warp waits; then acc += p * (sa * sb[col]) costs a multiply and an FMA.
-      auto promote_rowb = [&](float sa, const float* sbt) -> bool {
+      auto promote_rowb = [&](float sa, const float* sbt, bool from_smem) -> bool {
         static_assert(!ROWB || CHUNKS == 2, "row-scaled B is built for the 128-wide tile only");
         float4 sv[16];
+        if (from_smem) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) sv[i] = __ldg(reinterpret_cast<const float4*>(sbt) + i);
+          for (int i = 0; i < 16; ++i) sv[i] = reinterpret_cast<const float4*>(sbt)[i];   // same address in all lanes: broadcast
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sv[i] = __ldg(reinterpret_cast<const float4*>(sbt) + i);
+        }
         const uint32_t ts = it % TS;
         const uint32_t tph = (it / TS) & 1u;
         ++it;
@@ -616,6 +656,12 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       // The scales AsT[kb][row] and Bs[nb, kb] come from global memory (L2 latency of several
       // hundred clocks). They are fetched a whole group of PF K blocks ahead so that their
       // first use never stalls the promotion loop.
+      if constexpr (ROWB) {
+        if (args.rowb_table) {
+          ok = __all_sync(0xffffffffu, mbar_wait(sfull, rowb_tile & 1u, abort_flag, status_word));
+          if (!ok) break;
+        }
+      }
       constexpr int PF = (CHUNKS == 2) ? 2 : 4;
       float sa_c[PF], sb_c[PF], sa_n[PF], sb_n[PF];
       const int kb_last = seg.kb_end - 1;
@@ -637,7 +683,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         for (int j = 0; j < PF; ++j) {
           if (ok && kb0 + j < seg.kb_end) {
             if constexpr (ROWB) {
-              ok = promote_rowb(sa_c[j], args.BsT + static_cast<int64_t>(kb0 + j) * args.n_pad + col0);
+              ok = args.rowb_table
+                       ? promote_rowb(sa_c[j], rowb_table + (kb0 + j) * 128 + cw * Cfg::EPI_COLS, true)
+                       : promote_rowb(sa_c[j], args.BsT + static_cast<int64_t>(kb0 + j) * args.n_pad + col0, false);
             } else {
               ok = promote(sa_c[j] * sb_c[j]);
             }
@@ -650,6 +698,14 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         }
       }
       if (!ok) break;
+      if constexpr (ROWB) {
+        if (args.rowb_table) {
+          // done with this tile's scale table: the producer may load the next one
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sempty);
+          ++rowb_tile;
+        }
+      }
 
 #define ACC(i) (((i) & 1) ? acc[(i) >> 5][((i) & 31) >> 1].y : acc[(i) >> 5][((i) & 31) >> 1].x)
       if (SK && (seg.kb_begin != 0 || seg.kb_end != num_kb)) {
@@ -847,8 +903,8 @@ gemm_tile_decode_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 template <int BN>
 __global__ void __launch_bounds__(TileCfg<BN, false>::THREADS, 1)
 gemm_tile_rowb_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const GemmArgs args) {
-  gemm_tile_body<BN, false, 0, false, true>(tmap_a, tmap_b, args, nullptr);
+                      const __grid_constant__ CUtensorMap tmap_bst, const GemmArgs args) {
+  gemm_tile_body<BN, false, 0, false, true>(tmap_a, tmap_b, args, nullptr, &tmap_bst);
 }
 
 // Multicast form: args.dst[0] is a multimem address; every 128-byte row segment of a finished
@@ -896,36 +952,77 @@ tile_prep_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t
 }
 
 // Tail split-K: adds the K ranges of every tail tile (ascending range order: fixed, hence
-// bit-reproducible) and writes C. Grid = (tail tiles, 16 row chunks of 8 rows); BN threads,
-// one per tile column.
+// bit-reproducible) and writes C. Grid = (tail tiles, 4 chunks of 32 rows); 256 threads.
+// Phase 1: warp w sums the float4 column groups w, w + 8, ... of the chunk's 32 rows (lane = row:
+// 512 contiguous bytes per load in the partial-tile layout of sk_partial_ptr) and parks the sums
+// in shared memory; phase 2: warp w writes rows w, w + 8, ... with lane l holding columns
+// [8 l, 8 l + 8), so that C leaves in whole 512-byte (bf16) or 1-KiB (fp32) row segments.
 __global__ void __launch_bounds__(256)
 tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
-                     int out_fp32, int BN, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per) {
+                     int out_fp32, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per) {
+  constexpr int BN = 256;
+  constexpr int PITCH = BN + 1;                 // floats per staged row: column c of row r sits in bank (r + c) % 32
+  __shared__ float stage[32 * PITCH];
   int m_blk, n_blk;
   tile_coords(sk_full + static_cast<int>(blockIdx.x), num_m, num_n, m_blk, n_blk);
-  const int64_t col = static_cast<int64_t>(n_blk) * BN + threadIdx.x;
-  if (static_cast<int>(threadIdx.x) >= BN || col >= N) return;
-  const int r0 = blockIdx.y * 8;
-  float sum[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-  for (int j = 0; j < sk_split; ++j) {
-    if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
-    const int64_t slot = static_cast<int64_t>(blockIdx.x) * sk_split + j;
-    // element (row, column c) of a slot sits at float index ((c / 4) * 128 + row) * 4 + c % 4
-    const float* src = partial + ((slot * (BN / 4) + (threadIdx.x >> 2)) * 128 + r0) * 4 + (threadIdx.x & 3);
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (static_cast<int64_t>(m_blk) * 128 + r0 + i < M) sum[i] += __ldg(src + i * 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = blockIdx.y * 32;
+  const int64_t row0 = static_cast<int64_t>(m_blk) * 128 + r0;
+  if (row0 >= M) return;
+  for (int c4 = warp; c4 < BN / 4; c4 += 8) {
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < sk_split; ++j) {
+      if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
+      const int slot = static_cast<int>(blockIdx.x) * sk_split + j;
+      if (row0 + lane < M) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (static_cast<int64_t>(slot) * (BN / 4) + c4) * 128 + r0 + lane);
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+      }
+    }
+    float* dst = stage + lane * PITCH + c4 * 4;
+    dst[0] = sum.x;
+    dst[1] = sum.y;
+    dst[2] = sum.z;
+    dst[3] = sum.w;
   }
+  __syncthreads();
+  const int64_t col0 = static_cast<int64_t>(n_blk) * BN + lane * 8;
+  for (int r = warp; r < 32; r += 8) {
+    const int64_t row = row0 + r;
+    if (row >= M) break;
+    const float* src = stage + r * PITCH + lane * 8;
+    float v[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t row = static_cast<int64_t>(m_blk) * 128 + r0 + i;
-    if (row < M) {
-      if (out_fp32)
-        reinterpret_cast<float*>(C)[row * ldc + col] = sum[i];
-      else
-        reinterpret_cast<__nv_bfloat16*>(C)[row * ldc + col] = __float2bfloat16_rn(sum[i]);
+    for (int j = 0; j < 8; ++j) v[j] = src[j];
+    if (out_fp32) {
+      float* crow = reinterpret_cast<float*>(C) + row * ldc + col0;
+      if (col0 + 8 <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+        *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(crow + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col0 + j < N) crow[j] = v[j];
+      }
+    } else {
+      __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + row * ldc + col0;
+      if (col0 + 8 <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t*>(&p0);
+        u.y = *reinterpret_cast<uint32_t*>(&p1);
+        u.z = *reinterpret_cast<uint32_t*>(&p2);
+        u.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>(crow) = u;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col0 + j < N) crow[j] = __float2bfloat16_rn(v[j]);
+      }
     }
   }
 }

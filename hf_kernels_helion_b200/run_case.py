@@ -1,10 +1,11 @@
 """Run one shape of the hot path a few times and print its device time.
 
-    python -m hf_kernels_helion_b200.run_case <variant|quant> M N K [launches]
+    python -m hf_kernels_helion_b200.run_case <variant|quant|rowscale> M N K [launches]
 
-`variant` is a name from `_lib.VARIANT_NAMES` ("auto", "tile128", "tile256", "streamk", "tile256_sk") and runs
-`b200fp8_gemm` on random e4m3 operands with scales in [0.5, 1); "quant" runs the per-token-group activation
-quantiser on a random bf16 [M, K] matrix (N is ignored). The launches are back to back on one stream, so the
+`variant` is a name from `_lib.VARIANT_NAMES` ("auto", "tile128", "tile256", "streamk", "tile256_sk", "pair256",
+"pair256_split") and runs `b200fp8_gemm` on random e4m3 operands with scales in [0.5, 1); "rowscale" runs
+`b200fp8_gemm_rowscale` (one B scale per row of B); "quant" runs the per-token-group activation quantiser on a
+random bf16 [M, K] matrix (N is ignored). The launches are back to back on one stream, so the
 command is small enough to be wrapped by a profiler capture of a single kernel; the time printed is the mean
 over the launches after the first, measured with CUDA events.
 """
@@ -28,9 +29,16 @@ def main(argv):
         x = torch.randn(M, K, device=dev).to(torch.bfloat16)
         run = lambda: pkg.fp8_act_quant(x)
         work, unit = M * K * (2 + 1) + 4 * M * (K // 128), "GB/s"
+    elif variant == "rowscale":
+        A = (torch.randn(M, K, device=dev) * 0.3).to(torch.float8_e4m3fn)
+        B = (torch.randn(N, K, device=dev) * 0.3).to(torch.float8_e4m3fn)
+        As = torch.rand(M, K // 128, device=dev) * 0.5 + 0.5
+        Bs = torch.rand(N, K // 128, device=dev) * 0.5 + 0.5
+        run = lambda: runtime.gemm_rowscale(A, B, As, Bs, 128, torch.bfloat16)
+        work, unit = 2 * M * N * K, "TFLOP/s"
     else:
         if variant not in _lib.VARIANT_NAMES:
-            raise SystemExit(f"unknown variant {variant!r}; one of {sorted(_lib.VARIANT_NAMES)} or 'quant'")
+            raise SystemExit(f"unknown variant {variant!r}; one of {sorted(_lib.VARIANT_NAMES)}, 'rowscale' or 'quant'")
         A = (torch.randn(M, K, device=dev) * 0.3).to(torch.float8_e4m3fn)
         B = (torch.randn(N, K, device=dev) * 0.3).to(torch.float8_e4m3fn)
         As = torch.rand(M, K // 128, device=dev) * 0.5 + 0.5
