@@ -30,9 +30,11 @@ def test_golden_vectors_from_reference_source(device, name):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 384, 512), (130, 200, 320), (512, 512, 2048), (257, 1100, 1152),
-                                   (2048, 2048, 4096)])
+                                   (2048, 2048, 4096), (64, 512, 8192), (200, 384, 16384), (300, 40000, 256)])
 def test_rowscale_vs_oracle(device, M, N, K):
-    """Ragged M, N (not a multiple of 128) and K (last K block short); fp32 and bf16 results."""
+    """Ragged M, N (not a multiple of 128) and K (last K block short); fp32 and bf16 results. K <= 8192 keeps the
+    B scales of a tile in shared memory (64 K blocks exactly at K = 8192), K = 16384 is beyond that table and
+    reads them from global memory; N = 40000 gives every CTA more than one tile, so the table is recycled."""
     A, B, As, Bs = oracle.make_rowscale_inputs(M, N, K, M + N + K)
     ref = oracle.gemm_rowscale_dequant(A, B, As, Bs)
     d = [t.to(device) for t in (A, B, As, Bs)]
