@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -626,7 +627,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   auto fill_dst = [&](GemmArgs& a) {
     a.n_dst = n_dst;
     a.staged_store = staged ? 1 : 0;
-    a.mc_store = mc ? 1 : 0;
+    a.mc_store = mc ? 1 : (n_dst > 1 && getenv("B200FP8_EXP_LSU_SCATTER") != nullptr) ? 2 : 0;
     for (int d = 0; d < 8; ++d) {
       a.dst[d] = d < n_dst ? dst[d] : nullptr;
       a.dst_ld[d] = d < n_dst ? dst_ld[d] : 0;
@@ -654,13 +655,19 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   }
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
-  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, dev->sm_count);
+  const bool auto_variant = variant == B200FP8_VARIANT_AUTO;
+  if (auto_variant) variant = pick_variant(M, N, K, dev->sm_count);
   if (fq.rowb) variant = B200FP8_VARIANT_TILE128;   // the row-scaled promotion exists for the 128-wide tile only
   const bool multi = n_dst > 1 || mc;
   if (fq.rowb && (multi || fused_q)) return B200FP8_ERR_VARIANT;
+  // Several destinations (the N-sharded exchange): the pair kernel's smaller pipeline stages leave room
+  // for a second set of output staging buffers, which keeps NVLink busy through the next tile's K loop
+  if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
+  if (auto_variant && n_dst > 1 && !mc && getenv("B200FP8_EXP_LSU_SCATTER") == nullptr &&
+      variant == B200FP8_VARIANT_TILE256 && M > 128 && dev->pair_clusters > 0)
+    variant = B200FP8_VARIANT_PAIR256;
   const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT;
   if (pair && (mc || fq.rowb)) return B200FP8_ERR_VARIANT;
-  if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
   if (multi && !pair && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256)
     return B200FP8_ERR_VARIANT;
 

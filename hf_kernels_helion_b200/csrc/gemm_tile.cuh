@@ -5,9 +5,9 @@
 // Roles inside one CTA (one CTA per SM, tiles handed out round-robin):
 //   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per K block
 //               into a STAGES-deep shared-memory ring (SWIZZLE_128B, no multicast)
-//   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block into
-//               one of the TMEM accumulator stages, then tcgen05.commit to release the
-//               smem slot and to publish the TMEM stage
+//   warps 1, 3  MMA issuers, alternating K blocks: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per
+//               K block into one of the TMEM accumulator stages, then tcgen05.commit to release
+//               the smem slot and to publish the TMEM stage
 //   warp 2      TMEM allocation / deallocation
 //   warps 4..   promotion + epilogue: tcgen05.ld the fp32 partial of one K block,
 //               acc += partial * (As[row, kb] * Bs[nb, kb]) in registers (the block
@@ -15,6 +15,10 @@
 //               K blocks), and after the last K block convert and store the tile.
 // Several TMEM accumulator stages (512 / BN) let the MMAs of later K blocks overlap the
 // promotion of block k.
+// Forms of the same body (template parameters of gemm_tile_body): 128- or 256-wide tiles; a
+// multi-destination epilogue (TMA stores or multimem stores of every finished box into several
+// [M, N] buffers: the N-sharded multi-GPU exchange); tail split-K; row-scaled B; decode forms
+// with 16- or 64-row A slots; and CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -98,7 +102,9 @@ struct TileCfg {
   static constexpr int A_ROWS = A_ROWS_;
   static constexpr int HALVES = PAIR_ == 2 ? 2 : 1;       // separately signalled column halves of a K block
   static constexpr int B_ROWS = PAIR_ ? BN_ / 2 : BN_;    // rows of B per CTA and K block
-  static constexpr int STAGES = PAIR_ ? 6 : (A_ROWS_ == 16) ? 6 : (A_ROWS_ == 64) ? 5 : (BN_ == 128) ? 6 : 4;
+  // (pair kernels: 32-KiB stages; the multi-destination pair kernel gives one stage up for a second set of
+  // output staging buffers)
+  static constexpr int STAGES = PAIR_ ? (MULTI_ ? 5 : 6) : (A_ROWS_ == 16) ? 6 : (A_ROWS_ == 64) ? 5 : (BN_ == 128) ? 6 : 4;
   static_assert(PAIR_ == 0 || (BN_ == 256 && A_ROWS_ == 128), "pair kernels: 256-wide tiles, full A slots");
   static constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quarter
   static constexpr int EPI_COLS = BN_ / 2;          // accumulator columns (registers) per epilogue thread
@@ -131,8 +137,15 @@ struct TileCfg {
   static constexpr int TMEM_STAGES = 512 / BN_;     // accumulator stages in TMEM (all 512 columns are used)
   static constexpr int TMEM_COLS = TMEM_STAGES * BN_;
   static constexpr int BAR_BYTES = 256;
-  // output staging: each epilogue warp owns 32 rows x 128 bytes (128-byte-swizzled)
-  static constexpr int OUT_STAGE_BYTES_PER_WARP = 32 * 128;
+  // output staging: each epilogue warp owns OUT_BUFS boxes of 32 rows x 128 bytes (128-byte-swizzled).
+  // With ONE box a warp cannot stage the next 128-byte column group before the TMA has read the
+  // previous one out, i.e. before it has left over NVLink: the link idles during the next tile's K
+  // loop and the warp idles while the link drains. Two boxes (pair kernels, whose smaller pipeline
+  // stages leave the room) let a whole bf16 tile queue up behind the K loop of the next one: measured
+  // on 4 GPUs, 8192 x 18432 x 7168: see DESIGN.md.
+  static constexpr int OUT_BUFS = (MULTI_ && PAIR_) ? 2 : 1;
+  static constexpr int OUT_BOX_BYTES = 32 * 128;
+  static constexpr int OUT_STAGE_BYTES_PER_WARP = OUT_BOX_BYTES * OUT_BUFS;
   // (only the multi-destination kernel stages its output; the single-destination kernel
   // stores straight from registers and keeps the shared memory and registers for the main loop)
   static constexpr bool MULTI = MULTI_;
@@ -525,6 +538,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
     constexpr int CHUNKS = Cfg::EPI_COLS / 32;
     const uint32_t lane_col = (static_cast<uint32_t>(q * 32) << 16) + cw * Cfg::EPI_COLS;
     uint32_t it = 0;
+    uint32_t out_pass = 0;     // boxes this warp has staged so far (picks the staging buffer)
+    (void)out_pass;
     uint32_t rowb_tile = 0;
     (void)rowb_tile;
     bool ok = (warp & 3) < live_quarters;
@@ -721,7 +736,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         // Multi-destination and multicast forms: per pass, 128 bytes of each of this warp's 32 rows
         // go to the warp's staging area in the SWIZZLE_128B pattern (16-byte chunk index XOR
         // row % 8, conflict-free for the row-wise writes).
-        uint8_t* stage_w = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
+        uint8_t* stage_base = out_stage + (warp - 4) * Cfg::OUT_STAGE_BYTES_PER_WARP;
+        uint8_t* stage_w = stage_base;
         const int esize = args.out_fp32 ? 4 : 2;
         const int passes = Cfg::EPI_COLS * esize / 128;
         auto stage_pass = [&](int p) {
@@ -761,30 +777,43 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         if constexpr (MC) {
           // Multicast destination: eight lanes per row read the staged row back as 16-byte chunks, so
           // that every 128-byte row segment leaves as one contiguous multimem.st request.
+          // (mc_store == 2: the same row segments written with plain 16-byte stores to each of the n_dst
+          // destination buffers - peer stores that go through the load/store units, not the TMA unit)
           const int64_t n_bytes = N * esize;
-          uint8_t* mc_base = reinterpret_cast<uint8_t*>(args.dst[0]);
-          const int64_t ld_bytes = args.dst_ld[0] * esize;
           for (int p = 0; p < passes; ++p) {
             __syncwarp();                                // the previous pass has been read back
             stage_pass(p);
             __syncwarp();
             const int c = lane & 7;
             const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + c * 16;
-            int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
-            uint8_t* gptr = mc_base + grow * ld_bytes + col_byte;
             const bool col_ok = col_byte < n_bytes;
+            const int nd = args.mc_store == 2 ? args.n_dst : 1;
+            for (int d = 0; d < nd; ++d) {
+              const int64_t ld_bytes = args.dst_ld[d] * esize;
+              int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
+              uint8_t* gptr = reinterpret_cast<uint8_t*>(args.dst[d]) + grow * ld_bytes + col_byte;
 #pragma unroll 2
-            for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
-              const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
-              if (col_ok && grow < M) multimem_st_v4(gptr, v);
+              for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
+                if (col_ok && grow < M) {
+                  if (args.mc_store == 2) *reinterpret_cast<uint4*>(gptr) = v;
+                  else multimem_st_v4(gptr, v);
+                }
+              }
             }
           }
         } else {
           // One TMA store per destination ships the 32 x 128-byte box; rows and columns beyond
           // [M, N] are clipped by the TMA.
           for (int p = 0; p < passes; ++p) {
-            if (lane == 0) bulk_wait_group_read0();   // the previous box has left the staging buffer
+            // the box that last used this staging buffer has been read out by the TMA
+            if (lane == 0) {
+              if constexpr (Cfg::OUT_BUFS == 2) bulk_wait_group_read1();
+              else bulk_wait_group_read0();
+            }
             __syncwarp();
+            stage_w = stage_base + (out_pass % Cfg::OUT_BUFS) * Cfg::OUT_BOX_BYTES;
+            ++out_pass;
             stage_pass(p);
             // generic-proxy writes above -> visible to the async proxy, then one lane sends the
             // box to every destination; the copies run on while the warp goes back to the K loop

@@ -185,6 +185,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all committed groups of this thread have finished READING shared memory (it may be reused)
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the most recent committed group of this thread have finished reading shared memory
+__device__ __forceinline__ void bulk_wait_group_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // all committed groups of this thread are complete (their global writes are performed)
 // 16-byte store to a multimem (NVLink multicast) address: the switch replicates the write into
 // the memory of every GPU bound to the multicast object. The bits are not interpreted.
