@@ -7,7 +7,6 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -627,7 +626,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   auto fill_dst = [&](GemmArgs& a) {
     a.n_dst = n_dst;
     a.staged_store = staged ? 1 : 0;
-    a.mc_store = mc ? 1 : (n_dst > 1 && getenv("B200FP8_EXP_LSU_SCATTER") != nullptr) ? 2 : 0;
+    a.mc_store = mc ? 1 : 0;
     for (int d = 0; d < 8; ++d) {
       a.dst[d] = d < n_dst ? dst[d] : nullptr;
       a.dst_ld[d] = d < n_dst ? dst_ld[d] : 0;
@@ -663,8 +662,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   // Several destinations (the N-sharded exchange): the pair kernel's smaller pipeline stages leave room
   // for a second set of output staging buffers, which keeps NVLink busy through the next tile's K loop
   if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
-  if (auto_variant && n_dst > 1 && !mc && getenv("B200FP8_EXP_LSU_SCATTER") == nullptr &&
-      variant == B200FP8_VARIANT_TILE256 && M > 128 && dev->pair_clusters > 0)
+  if (auto_variant && n_dst > 1 && !mc && variant == B200FP8_VARIANT_TILE256 && M > 128 && dev->pair_clusters > 0)
     variant = B200FP8_VARIANT_PAIR256;
   const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT;
   if (pair && (mc || fq.rowb)) return B200FP8_ERR_VARIANT;

@@ -141,8 +141,8 @@ struct TileCfg {
   // With ONE box a warp cannot stage the next 128-byte column group before the TMA has read the
   // previous one out, i.e. before it has left over NVLink: the link idles during the next tile's K
   // loop and the warp idles while the link drains. Two boxes (pair kernels, whose smaller pipeline
-  // stages leave the room) let a whole bf16 tile queue up behind the K loop of the next one: measured
-  // on 4 GPUs, 8192 x 18432 x 7168: see DESIGN.md.
+  // stages leave the room) let a whole bf16 tile queue up behind the K loop of the next one. Measured,
+  // 8192 x 18432 x 7168 N-sharded: 2 GPUs 590 vs 611 us for the single-CTA form with one box; 4 GPUs 538 vs 540.
   static constexpr int OUT_BUFS = (MULTI_ && PAIR_) ? 2 : 1;
   static constexpr int OUT_BOX_BYTES = 32 * 128;
   static constexpr int OUT_STAGE_BYTES_PER_WARP = OUT_BOX_BYTES * OUT_BUFS;
@@ -777,29 +777,22 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
         if constexpr (MC) {
           // Multicast destination: eight lanes per row read the staged row back as 16-byte chunks, so
           // that every 128-byte row segment leaves as one contiguous multimem.st request.
-          // (mc_store == 2: the same row segments written with plain 16-byte stores to each of the n_dst
-          // destination buffers - peer stores that go through the load/store units, not the TMA unit)
           const int64_t n_bytes = N * esize;
+          uint8_t* mc_base = reinterpret_cast<uint8_t*>(args.dst[0]);
+          const int64_t ld_bytes = args.dst_ld[0] * esize;
           for (int p = 0; p < passes; ++p) {
             __syncwarp();                                // the previous pass has been read back
             stage_pass(p);
             __syncwarp();
             const int c = lane & 7;
             const int64_t col_byte = static_cast<int64_t>(col0) * esize + p * 128 + c * 16;
+            int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
+            uint8_t* gptr = mc_base + grow * ld_bytes + col_byte;
             const bool col_ok = col_byte < n_bytes;
-            const int nd = args.mc_store == 2 ? args.n_dst : 1;
-            for (int d = 0; d < nd; ++d) {
-              const int64_t ld_bytes = args.dst_ld[d] * esize;
-              int64_t grow = static_cast<int64_t>(m0) + q * 32 + (lane >> 3);
-              uint8_t* gptr = reinterpret_cast<uint8_t*>(args.dst[d]) + grow * ld_bytes + col_byte;
 #pragma unroll 2
-              for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
-                const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
-                if (col_ok && grow < M) {
-                  if (args.mc_store == 2) *reinterpret_cast<uint4*>(gptr) = v;
-                  else multimem_st_v4(gptr, v);
-                }
-              }
+            for (int r = lane >> 3; r < 32; r += 4, grow += 4, gptr += 4 * ld_bytes) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage_w + r * 128 + ((c ^ (r & 7)) << 4));
+              if (col_ok && grow < M) multimem_st_v4(gptr, v);
             }
           }
         } else {
