@@ -364,6 +364,11 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
       // dependent launch), the weight loads of the first K blocks do not wait for it: they are issued
       // at once, the A loads of those stages follow after griddepcontrol.wait.
       bool a_pending = args.a_from_prep != 0;
+      if constexpr (PAIR) {
+        // (pair kernels are not the decode path: they simply wait before their first load)
+        if (a_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
+        a_pending = false;
+      }
       uint32_t tile_no = 0;
       (void)tile_no;
       uint32_t pend_from = 0;
