@@ -620,10 +620,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
             const float4 s4 = sv[c >> 2];
             const float s_lo = (c & 2) ? s4.z : s4.x;
             const float s_hi = (c & 2) ? s4.w : s4.y;
-            const float p_lo = __uint_as_float(g ? pb[2 * j] : pa[2 * j]);
-            const float p_hi = __uint_as_float(g ? pb[2 * j + 1] : pa[2 * j + 1]);
-            acc[g & (CHUNKS - 1)][j].x = fmaf(p_lo, sa * s_lo, acc[g & (CHUNKS - 1)][j].x);
-            acc[g & (CHUNKS - 1)][j].y = fmaf(p_hi, sa * s_hi, acc[g & (CHUNKS - 1)][j].y);
+            // two columns at a time: (sa * s_lo, sa * s_hi) and the accumulation are one packed instruction each
+            ffma2(acc[g & (CHUNKS - 1)][j], g ? pb[2 * j] : pa[2 * j], g ? pb[2 * j + 1] : pa[2 * j + 1],
+                  fmul2_bcast(s_lo, s_hi, sa));
           }
         }
         return true;

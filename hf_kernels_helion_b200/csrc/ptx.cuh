@@ -345,9 +345,29 @@ __device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
       : "memory");
 }
 
-// acc[0..31] += p[0..31] * s (acc kept as pairs of adjacent columns).
+// acc (two adjacent columns) += (plo, phi) * (s, s) as ONE packed fma.rn.f32x2.
+__device__ __forceinline__ void ffma2(float2& acc, uint32_t plo, uint32_t phi, uint64_t ss) {
+  uint64_t a, pp;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(acc.x), "f"(acc.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pp) : "r"(plo), "r"(phi));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a) : "l"(pp), "l"(ss));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(acc.x), "=f"(acc.y) : "l"(a));
+}
+
+// (a, b) * (c, c) as one packed multiply: both halves of a 64-bit register pair.
+__device__ __forceinline__ uint64_t fmul2_bcast(float a, float b, float c) {
+  uint64_t ab, cc, r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ab) : "f"(a), "f"(b));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(ab), "l"(cc));
+  return r;
+}
+
+// acc[0..31] += p[0..31] * s (acc kept as pairs of adjacent columns). Scalar FFMA on purpose: in the
+// 128-wide kernels, whose promotion keeps two TMEM loads in flight, the packed form measured 7 %
+// slower (182 vs 169 us at 4096 x 4096 x 8192, alternating processes); the 256-wide promotion
+// (fma64_scalar) is the other way round.
 __device__ __forceinline__ void fma32_scalar(float2 (&acc)[16], const uint32_t (&p)[32], float s) {
-  // plain FFMA: measured faster here than fma.rn.f32x2 (3 issue clocks per packed pair)
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     acc[j].x = fmaf(__uint_as_float(p[2 * j]), s, acc[j].x);
@@ -402,18 +422,18 @@ __device__ __forceinline__ void tmem_ld_wait_64(uint32_t (&r)[64]) {
       : "memory");
 }
 
-// acc_lo[0..31] += p[0..31] * s, acc_hi[0..31] += p[32..63] * s
+// acc_lo[0..31] += p[0..31] * s, acc_hi[0..31] += p[32..63] * s, with packed FMAs: half the
+// instructions of the scalar form. In a burst of launches the two forms time the same (the loop
+// is bound by the accumulator round trip, not by FMA issue); over seconds under the 1 kW power
+// cap the packed form sustains 1.3 % more (1702-1705 vs 1680-1684 TFLOP/s, 8192 x 18432 x 7168,
+// alternating 2-second runs): fewer instructions issued for the same arithmetic.
 __device__ __forceinline__ void fma64_scalar(float2 (&acc_lo)[16], float2 (&acc_hi)[16], const uint32_t (&p)[64], float s) {
+  uint64_t ss;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(ss) : "f"(s));
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    acc_lo[j].x = fmaf(__uint_as_float(p[2 * j]), s, acc_lo[j].x);
-    acc_lo[j].y = fmaf(__uint_as_float(p[2 * j + 1]), s, acc_lo[j].y);
-  }
+  for (int j = 0; j < 16; ++j) ffma2(acc_lo[j], p[2 * j], p[2 * j + 1], ss);
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    acc_hi[j].x = fmaf(__uint_as_float(p[32 + 2 * j]), s, acc_hi[j].x);
-    acc_hi[j].y = fmaf(__uint_as_float(p[32 + 2 * j + 1]), s, acc_hi[j].y);
-  }
+  for (int j = 0; j < 16; ++j) ffma2(acc_hi[j], p[32 + 2 * j], p[32 + 2 * j + 1], ss);
 }
 
 }  // namespace b200fp8
