@@ -345,23 +345,17 @@ __device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
       : "memory");
 }
 
-// acc (two adjacent columns) += (plo, phi) * (s, s) as ONE packed fma.rn.f32x2.
-__device__ __forceinline__ void ffma2(float2& acc, uint32_t plo, uint32_t phi, uint64_t ss) {
-  uint64_t a, pp;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(acc.x), "f"(acc.y));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(pp) : "r"(plo), "r"(phi));
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a) : "l"(pp), "l"(ss));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(acc.x), "=f"(acc.y) : "l"(a));
+// acc (two adjacent columns) += (plo, phi) * ss as ONE packed fma.rn.f32x2 (compiler intrinsic of
+// sm_100; the same code and speed as the instruction written as inline PTX).
+typedef float2 fpair_t;
+__device__ __forceinline__ void ffma2(float2& acc, uint32_t plo, uint32_t phi, float2 ss) {
+  acc = __ffma2_rn(make_float2(__uint_as_float(plo), __uint_as_float(phi)), ss, acc);
 }
-
-// (a, b) * (c, c) as one packed multiply: both halves of a 64-bit register pair.
-__device__ __forceinline__ uint64_t fmul2_bcast(float a, float b, float c) {
-  uint64_t ab, cc, r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(ab) : "f"(a), "f"(b));
-  asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c));
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(ab), "l"(cc));
-  return r;
+// (a, b) * (c, c) as one packed multiply.
+__device__ __forceinline__ float2 fmul2_bcast(float a, float b, float c) {
+  return __fmul2_rn(make_float2(a, b), make_float2(c, c));
 }
+__device__ __forceinline__ float2 fpack2(float s) { return make_float2(s, s); }
 
 // acc[0..31] += p[0..31] * s (acc kept as pairs of adjacent columns). Scalar FFMA on purpose: in the
 // 128-wide kernels, whose promotion keeps two TMEM loads in flight, the packed form measured 7 %
@@ -428,8 +422,7 @@ __device__ __forceinline__ void tmem_ld_wait_64(uint32_t (&r)[64]) {
 // cap the packed form sustains 1.3 % more (1702-1705 vs 1680-1684 TFLOP/s, 8192 x 18432 x 7168,
 // alternating 2-second runs): fewer instructions issued for the same arithmetic.
 __device__ __forceinline__ void fma64_scalar(float2 (&acc_lo)[16], float2 (&acc_hi)[16], const uint32_t (&p)[64], float s) {
-  uint64_t ss;
-  asm("mov.b64 %0, {%1, %1};" : "=l"(ss) : "f"(s));
+  const fpair_t ss = fpack2(s);
 #pragma unroll
   for (int j = 0; j < 16; ++j) ffma2(acc_lo[j], p[2 * j], p[2 * j + 1], ss);
 #pragma unroll
