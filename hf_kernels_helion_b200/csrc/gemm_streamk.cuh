@@ -262,7 +262,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if constexpr (EC == 16) {
         uint32_t p[16];
         tmem_ld_32x16(taddr, p);
-        tmem_ld_wait();
+        tmem_ld_wait_16(p);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[ts]);
@@ -279,7 +279,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         for (int c = 0; c < EC; c += 32) {
           uint32_t p[32];
           tmem_ld_32x32(taddr + c, p);
-          tmem_ld_wait();
+          tmem_ld_wait_32(p);
           if (c + 32 == EC) {
             // The TMEM stage is handed back before the scale reads below. The MMA warp
             // can then run at most TS units ahead of this warp and the producer at most
