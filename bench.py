@@ -613,8 +613,12 @@ def main_ours(args):
         gemm_flops = 2.0 * M * n_local * K
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
         variant = _lib.load().b200fp8_gemm_pick_variant(M, n_local, K)
-        kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_kernel<256>", 3: "gemm_streamk_kernel",
-                  4: "gemm_tile_kernel<256> with tail split-K", 5: "gemm_pair_kernel", 6: "gemm_pair_kernel (split)"}[variant]
+        # (the 256-wide forms stage their output and store it by TMA: the *_multi_kernel instantiations, one destination at N = 1)
+        kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_multi_kernel<256>", 3: "gemm_streamk_kernel",
+                  4: "gemm_tile_kernel<256> with tail split-K", 5: "gemm_pair_multi_kernel<false>",
+                  6: "gemm_pair_multi_kernel<true>"}[variant]
+        if world > 1 and args.exchange == "fused" and variant == 2 and M > 128:
+            kernel = "gemm_pair_multi_kernel<false>"   # several destinations: AUTO takes the pair form whenever M > 128
         # DRAM bytes of one GEMM launch at 1 GPU, from one profiler capture of this kernel on this shape
         # (dram__bytes_read.sum / dram__bytes_write.sum); at N > 1 scaled by the share of the weight and of
         # the output a rank touches (A is read whole by every rank). Not re-measured by this run.

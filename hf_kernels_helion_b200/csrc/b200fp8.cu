@@ -319,7 +319,7 @@ double wave_efficiency(int64_t tiles, int sms) {
   return static_cast<double>(tiles) / static_cast<double>(waves * sms);
 }
 
-int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
+int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool pair_ok) {
   // Decode shapes (M <= 256) are weight-streaming and HBM-bound. Measured on B200 at N = 28672,
   // K = 8192: the plain 128x256 tile kernel (46 us at M = 16, 5.1 TB/s with 112 of 148 SMs busy)
   // beats the swap-AB stream-K kernel (65 us), so AUTO does not pick that one.
@@ -329,6 +329,11 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count) {
   const double e256 = wave_efficiency(num_m * ((N + 255) / 256), sm_count);
   // the 128x256 tile moves 25 % fewer operand bytes per flop; prefer it unless the last wave is much emptier
   if (e256 * 1.15 < e128) return B200FP8_VARIANT_TILE128;
+  // CTA pairs on 256 x 256 tiles with the output staged through shared memory and written by TMA
+  // (two staging sets per warp): the same tile waves as the single-CTA form when the number of
+  // M-blocks is even, and measured faster than it and than its tail split-K form (8192 x 18432 x 7168:
+  // 1.034 vs 1.11 ms, 1790 vs 1674 TFLOP/s sustained over 2.4 s; 4096 x 4096 x 8192: 141.3 vs 145.3 us)
+  if (pair_ok && num_m % 2 == 0) return B200FP8_VARIANT_PAIR256;
   // A mostly empty last wave is worth splitting along K, but the split-K kernel runs its
   // whole-tile part about 5 % slower (measured) and adds a fix-up pass: only take it when the
   // idle share of the last wave is at least a tenth of the whole run.
@@ -389,8 +394,11 @@ int launch_tile(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   } else if (args.mc_store) {
     cfg.dynamicSmemBytes = TileCfg<BN, true>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_tile_mc_kernel<BN>, ta, tb, args);
-  } else if (args.n_dst > 1) {
-    // one byte-matrix tensor map per destination: [M rows, N * element size], 32 x 128-byte boxes
+  } else if (args.n_dst > 1 || (BN == 256 && args.staged_store)) {
+    // Several destinations, and the 256-wide tile with one: the output leaves through shared memory
+    // and TMA stores instead of 16-byte stores of row pieces from registers (32 sectors per warp
+    // instruction), which shortens the stretch at the end of a tile in which nothing drains TMEM.
+    // One byte-matrix tensor map per destination: [M rows, N * element size], 32 x 128-byte boxes
     DstMaps dm;
     const int64_t esize = args.out_fp32 ? 4 : 2;
     for (int d = 0; d < 8; ++d) {
@@ -438,7 +446,7 @@ int launch_pair(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   cudaError_t err;
-  if (args.n_dst > 1) {
+  if (args.n_dst > 1 || args.staged_store) {
     DstMaps dm;
     const int64_t esize = args.out_fp32 ? 4 : 2;
     for (int d = 0; d < 8; ++d) {
@@ -560,12 +568,14 @@ int b200fp8_gemm_pair_clusters(void) {
   return d->pair_clusters;
 }
 
-int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) { return pick_variant(M, N, K, sm_count_or_default()); }
+int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) {
+  return pick_variant(M, N, K, sm_count_or_default(), b200fp8_gemm_pair_clusters() > 0);
+}
 
 int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   const int sms = sm_count_or_default();
-  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
+  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms, false);   // covers the pair form too (it needs less)
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
     return tile_workspace_bytes(M, K);
@@ -655,7 +665,8 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   if (M > 0x7FFFFF00 || N > 0x7FFFFF00 || K > 0x7FFFFF00) return B200FP8_ERR_TOO_LARGE;
 
   const bool auto_variant = variant == B200FP8_VARIANT_AUTO;
-  if (auto_variant) variant = pick_variant(M, N, K, dev->sm_count);
+  // (the pair form only pays with the staged output: a destination that cannot take 16-byte rows gets the single-CTA choice)
+  if (auto_variant) variant = pick_variant(M, N, K, dev->sm_count, dev->pair_clusters > 0 && staged && !mc && !fq.rowb);
   if (fq.rowb) variant = B200FP8_VARIANT_TILE128;   // the row-scaled promotion exists for the 128-wide tile only
   const bool multi = n_dst > 1 || mc;
   if (fq.rowb && (multi || fused_q)) return B200FP8_ERR_VARIANT;
@@ -840,7 +851,7 @@ int64_t b200fp8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int vari
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   if (M == 0 || N == 0 || K == 0) return 0;
   const int sms = sm_count_or_default();
-  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms);
+  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms, false);   // covers the pair form too (it needs less)
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
     return linear_prefix_bytes(M, K);
