@@ -146,8 +146,11 @@ struct TileCfg {
   static constexpr int OUT_BUFS = (MULTI_ && PAIR_) ? 2 : 1;
   static constexpr int OUT_BOX_BYTES = 32 * 128;
   static constexpr int OUT_STAGE_BYTES_PER_WARP = OUT_BOX_BYTES * OUT_BUFS;
-  // (only the multi-destination kernel stages its output; the single-destination kernel
-  // stores straight from registers and keeps the shared memory and registers for the main loop)
+  // (MULTI_ instantiations stage their output; the host takes them for several destinations and,
+  // for the 256-wide tile, also for one destination whose rows are 16-byte aligned: the staged tile
+  // leaves by TMA while the next K loop runs, where register stores of row pieces - 32 sectors per
+  // warp instruction - keep the promotion warps away from TMEM at the end of every tile. The other
+  // instantiations store straight from registers.)
   static constexpr bool MULTI = MULTI_;
   static constexpr int OUT_STAGE_BYTES = MULTI_ ? EPI_WARPS * OUT_STAGE_BYTES_PER_WARP : 0;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + BAR_BYTES + 1024;  // +1024: alignment slack
