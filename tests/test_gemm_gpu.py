@@ -250,8 +250,29 @@ def test_torch_compile_traces_the_op(device):
     assert torch.equal(f(A, B, As, Bs), eager)
 
 
-@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk"])
-@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (5, 256, 1024), (16, 1280, 2048), (130, 384, 256), (640, 4096, 1024)])
+def test_auto_takes_cta_pairs_where_they_pay(device):
+    """AUTO = 256 x 256 tiles on CTA pairs for M > 256 with an even number of 128-row blocks, when the
+    destination takes 16-byte rows (the output is then staged and stored by TMA); otherwise the
+    single-CTA choice. Either way the bits are those of the single-CTA kernel."""
+    lib = _lib.load()
+    pair = _lib.VARIANT_NAMES["pair256"]
+    assert lib.b200fp8_gemm_pair_clusters() > 0
+    assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == pair
+    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == pair
+    assert lib.b200fp8_gemm_pick_variant(640, 4096, 1024) != pair      # five row blocks
+    assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == _lib.VARIANT_TILE256
+    for (M, N, K) in [(512, 1024, 640), (512, 1100, 640), (1000, 520, 384)]:   # 1100 bf16 columns: rows not 16-byte multiples
+        A, B, As, Bs = _dev(oracle.make_quantised_inputs(M, N, K, M + N), device)
+        for dtype in (torch.bfloat16, torch.float32):
+            auto = runtime.gemm(A, B, As, Bs, 128, 128, dtype, variant="auto")
+            single = runtime.gemm(A, B, As, Bs, 128, 128, dtype, variant="tile256")
+            assert torch.equal(auto, single)
+    runtime.check_device_status()
+
+
+@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk", "pair256"])
+@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (5, 256, 1024), (16, 1280, 2048), (130, 384, 256), (640, 4096, 1024),
+                                   (512, 1024, 1024)])   # the last one: an even number of row blocks, AUTO = CTA pairs
 def test_fused_quantise_and_multiply_equals_the_two_calls(device, M, N, K, variant):
     """b200fp8_linear (activations quantised by the GEMM's own prep launch, straight into the
     kernel's input layout) must give the bits of b200fp8_quant_act followed by b200fp8_gemm."""
