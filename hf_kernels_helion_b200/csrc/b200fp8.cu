@@ -332,8 +332,10 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool pair_ok) {
   // CTA pairs on 256 x 256 tiles with the output staged through shared memory and written by TMA
   // (two staging sets per warp): the same tile waves as the single-CTA form when the number of
   // M-blocks is even, and measured faster than it and than its tail split-K form (8192 x 18432 x 7168:
-  // 1.034 vs 1.11 ms, 1790 vs 1674 TFLOP/s sustained over 2.4 s; 4096 x 4096 x 8192: 141.3 vs 145.3 us)
-  if (pair_ok && num_m % 2 == 0) return B200FP8_VARIANT_PAIR256;
+  // 1.034 vs 1.11 ms, 1790 vs 1674 TFLOP/s sustained over 2.4 s; 4096 x 4096 x 8192: 141.3 vs 145.3 us).
+  // With the stores out of the way the form that issues each K block as two 128-column halves is the
+  // faster of the two pair kernels (same shapes: 1.002 vs 1.016 ms, 1846 vs 1811 sustained; 136.2 vs 139.4 us).
+  if (pair_ok && num_m % 2 == 0) return B200FP8_VARIANT_PAIR256_SPLIT;
   // A mostly empty last wave is worth splitting along K, but the split-K kernel runs its
   // whole-tile part about 5 % slower (measured) and adds a fix-up pass: only take it when the
   // idle share of the last wave is at least a tenth of the whole run.
@@ -673,8 +675,9 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   // Several destinations (the N-sharded exchange): the pair kernel's smaller pipeline stages leave room
   // for a second set of output staging buffers, which keeps NVLink busy through the next tile's K loop
   if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
-  if (auto_variant && n_dst > 1 && !mc && variant == B200FP8_VARIANT_TILE256 && M > 128 && dev->pair_clusters > 0)
-    variant = B200FP8_VARIANT_PAIR256;
+  if (auto_variant && n_dst > 1 && !mc && M > 128 && dev->pair_clusters > 0 &&
+      (variant == B200FP8_VARIANT_TILE256 || variant == B200FP8_VARIANT_PAIR256_SPLIT))
+    variant = B200FP8_VARIANT_PAIR256;   // (the exchange was measured and tuned with the unsplit form)
   const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT;
   if (pair && (mc || fq.rowb)) return B200FP8_ERR_VARIANT;
   if (multi && !pair && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256)

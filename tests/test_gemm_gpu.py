@@ -255,7 +255,7 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     destination takes 16-byte rows (the output is then staged and stored by TMA); otherwise the
     single-CTA choice. Either way the bits are those of the single-CTA kernel."""
     lib = _lib.load()
-    pair = _lib.VARIANT_NAMES["pair256"]
+    pair = _lib.VARIANT_NAMES["pair256_split"]
     assert lib.b200fp8_gemm_pair_clusters() > 0
     assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == pair
     assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == pair
@@ -270,7 +270,7 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     runtime.check_device_status()
 
 
-@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk", "pair256"])
+@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk", "pair256", "pair256_split"])
 @pytest.mark.parametrize("M,N,K", [(1, 384, 512), (5, 256, 1024), (16, 1280, 2048), (130, 384, 256), (640, 4096, 1024),
                                    (512, 1024, 1024)])   # the last one: an even number of row blocks, AUTO = CTA pairs
 def test_fused_quantise_and_multiply_equals_the_two_calls(device, M, N, K, variant):
