@@ -323,7 +323,9 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool pair_ok) {
   // Decode shapes (M <= 256) are weight-streaming and HBM-bound. Measured on B200 at N = 28672,
   // K = 8192: the plain 128x256 tile kernel (46 us at M = 16, 5.1 TB/s with 112 of 148 SMs busy)
   // beats the swap-AB stream-K kernel (65 us), so AUTO does not pick that one.
-  if (M <= 256) return (N > 128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
+  // (two row blocks, M in 129..256, go to the CTA pairs below when the device runs them: 79.5 vs 84-86 us at M = 256)
+  if (M <= 128 || (M <= 256 && (N <= 128 || !pair_ok)))
+    return (N > 128) ? B200FP8_VARIANT_TILE256 : B200FP8_VARIANT_TILE128;
   const int64_t num_m = (M + 127) / 128;
   const double e128 = wave_efficiency(num_m * ((N + 127) / 128), sm_count);
   const double e256 = wave_efficiency(num_m * ((N + 255) / 256), sm_count);

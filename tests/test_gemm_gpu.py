@@ -125,7 +125,8 @@ def test_decode_shapes_full_size(device, M):
         ref_auto = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="auto")
         assert oracle.max_err_over_rms(alt.cpu(), ref_auto.cpu()) <= FP32_TOL
     out = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="auto")
-    assert _lib.load().b200fp8_gemm_pick_variant(M, N, K) == _lib.VARIANT_TILE256
+    # one row block: the single-CTA tile kernel; two: 256 x 256 tiles on CTA pairs
+    assert _lib.load().b200fp8_gemm_pick_variant(M, N, K) == (_lib.VARIANT_TILE256 if M <= 128 else _lib.VARIANT_NAMES["pair256_split"])
     runtime.check_device_status()
     g = torch.Generator().manual_seed(M)
     blocks = torch.randperm(N // 128, generator=g)[:6].tolist()
@@ -260,7 +261,9 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == pair
     assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == pair
     assert lib.b200fp8_gemm_pick_variant(640, 4096, 1024) != pair      # five row blocks
-    assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == _lib.VARIANT_TILE256
+    assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == pair
+    assert lib.b200fp8_gemm_pick_variant(128, 28672, 8192) == _lib.VARIANT_TILE256
+    assert lib.b200fp8_gemm_pick_variant(200, 128, 512) == _lib.VARIANT_NAMES["tile128"]
     for (M, N, K) in [(512, 1024, 640), (512, 1100, 640), (1000, 520, 384)]:   # 1100 bf16 columns: rows not 16-byte multiples
         A, B, As, Bs = _dev(oracle.make_quantised_inputs(M, N, K, M + N), device)
         for dtype in (torch.bfloat16, torch.float32):
