@@ -617,8 +617,8 @@ def main_ours(args):
         kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_multi_kernel<256>", 3: "gemm_streamk_kernel",
                   4: "gemm_tile_kernel<256> with tail split-K", 5: "gemm_pair_multi_kernel<false>",
                   6: "gemm_pair_multi_kernel<true>"}[variant]
-        if world > 1 and args.exchange == "fused" and variant in (2, 6) and M > 128:
-            kernel = "gemm_pair_multi_kernel<false>"   # several destinations: AUTO takes the pair form whenever M > 128
+        if world > 1 and args.exchange == "fused" and variant == 2 and M > 128:
+            kernel = "gemm_pair_multi_kernel<true>"   # several destinations: AUTO takes the pair form whenever M > 128
         # DRAM bytes of one GEMM launch at 1 GPU, from one profiler capture of this kernel on this shape
         # (dram__bytes_read.sum / dram__bytes_write.sum); at N > 1 scaled by the share of the weight and of
         # the output a rank touches (A is read whole by every rank). Not re-measured by this run.
