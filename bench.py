@@ -616,7 +616,7 @@ def main_ours(args):
         # (the 256-wide forms stage their output and store it by TMA: the *_multi_kernel instantiations, one destination at N = 1)
         kernel = {1: "gemm_tile_kernel<128>", 2: "gemm_tile_multi_kernel<256>", 3: "gemm_streamk_kernel",
                   4: "gemm_tile_kernel<256> with tail split-K", 5: "gemm_pair_multi_kernel<false>",
-                  6: "gemm_pair_multi_kernel<true>"}[variant]
+                  6: "gemm_pair_multi_kernel<true>", 7: "gemm_pair_multi_sk_kernel"}[variant]
         if world > 1 and args.exchange == "fused" and variant == 2 and M > 128:
             kernel = "gemm_pair_multi_kernel<true>"   # several destinations: AUTO takes the pair form whenever M > 128
         # DRAM bytes of one GEMM launch at 1 GPU, from one profiler capture of this kernel on this shape

@@ -14,7 +14,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libb200fp8.so"
 OUT_BF16, OUT_FP32 = 0, 1
 VARIANT_AUTO, VARIANT_TILE128, VARIANT_TILE256, VARIANT_STREAMK, VARIANT_TILE256_SK = 0, 1, 2, 3, 4
 VARIANT_PAIR256, VARIANT_PAIR256_SPLIT = 5, 6
-VARIANT_NAMES = {"auto": 0, "tile128": 1, "tile256": 2, "streamk": 3, "tile256_sk": 4, "pair256": 5, "pair256_split": 6}
+VARIANT_NAMES = {"auto": 0, "tile128": 1, "tile256": 2, "streamk": 3, "tile256_sk": 4, "pair256": 5, "pair256_split": 6,
+                 "pair256_split_sk": 7}
 
 # name -> (restype, argtypes); mirrors include/b200fp8.h one to one
 SIGNATURES = {

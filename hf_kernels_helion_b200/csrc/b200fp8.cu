@@ -94,6 +94,7 @@ int device_info(const DeviceInfo** out) {
       opt_in(reinterpret_cast<const void*>(&gemm_pair_kernel<true>), PairCfg::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<false>), PairMultiCfg::SMEM_BYTES);
       opt_in(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<true>), PairMultiCfg::SMEM_BYTES);
+      opt_in(reinterpret_cast<const void*>(&gemm_pair_multi_sk_kernel), PairMultiCfg::SMEM_BYTES);
       regs_ok(reinterpret_cast<const void*>(&gemm_pair_kernel<false>), PairCfg::THREADS,
               128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_pair_kernel<true>), PairCfg::THREADS,
@@ -101,6 +102,8 @@ int device_info(const DeviceInfo** out) {
       regs_ok(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<false>), PairCfg::THREADS,
               128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
       regs_ok(reinterpret_cast<const void*>(&gemm_pair_multi_kernel<true>), PairCfg::THREADS,
+              128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
+      regs_ok(reinterpret_cast<const void*>(&gemm_pair_multi_sk_kernel), PairCfg::THREADS,
               128 * PairCfg::REGS_CONTROL + 256 * PairCfg::REGS_EPILOGUE);
       if (ok) {
         // how many CTA pairs fit on the device at once (one CTA per SM; not every SM need be pairable)
@@ -313,13 +316,35 @@ TileSkPlan tile_sk_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
   return p;
 }
 
+// The same for 256 x 256 tiles on CTA pairs (B200FP8_VARIANT_PAIR256_SPLIT_SK): the workers are the pairs,
+// and every K range leaves two partial tiles (one per CTA of the pair).
+TileSkPlan pair_sk_plan(int64_t M, int64_t N, int64_t K, int pairs) {
+  TileSkPlan p;
+  p.num_m = static_cast<int>((M + 255) / 256);
+  p.num_n = static_cast<int>((N + 255) / 256);
+  p.num_kb = static_cast<int>((K + 127) / 128);
+  const int64_t tiles = static_cast<int64_t>(p.num_m) * p.num_n;
+  if (pairs < 1) pairs = 1;
+  p.grid = 2 * static_cast<int64_t>(pairs);
+  p.full = static_cast<int>((tiles / pairs) * pairs);
+  p.tail = static_cast<int>(tiles - p.full);
+  p.split = p.tail > 0 ? pairs / p.tail : 1;
+  if (p.split > p.num_kb / 4) p.split = p.num_kb / 4;   // keep ranges of at least 4 K blocks
+  if (p.split < 1) p.split = 1;
+  p.kb_per = (p.num_kb + p.split - 1) / p.split;
+  p.ast_bytes = tile_workspace_bytes(M, K);
+  p.partial_bytes = p.split >= 2 ? static_cast<int64_t>(p.tail) * p.split * 2 * 128 * 256 * 4 : 0;
+  return p;
+}
+
 double wave_efficiency(int64_t tiles, int sms) {
   if (tiles <= 0) return 1.0;
   const int64_t waves = (tiles + sms - 1) / sms;
   return static_cast<double>(tiles) / static_cast<double>(waves * sms);
 }
 
-int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool pair_ok) {
+int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, int pairs) {
+  const bool pair_ok = pairs > 0;
   // Decode shapes (M <= 256) are weight-streaming and HBM-bound. Measured on B200 at N = 28672,
   // K = 8192: the plain 128x256 tile kernel (46 us at M = 16, 5.1 TB/s with 112 of 148 SMs busy)
   // beats the swap-AB stream-K kernel (65 us), so AUTO does not pick that one.
@@ -337,7 +362,13 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, bool pair_ok) {
   // 1.034 vs 1.11 ms, 1790 vs 1674 TFLOP/s sustained over 2.4 s; 4096 x 4096 x 8192: 141.3 vs 145.3 us).
   // With the stores out of the way the form that issues each K block as two 128-column halves is the
   // faster of the two pair kernels (same shapes: 1.002 vs 1.016 ms, 1846 vs 1811 sustained; 136.2 vs 139.4 us).
-  if (pair_ok && num_m % 2 == 0) return B200FP8_VARIANT_PAIR256_SPLIT;
+  if (pair_ok && num_m % 2 == 0) {
+    // a mostly empty last wave of pair tiles is split along K under the same rule as below
+    const TileSkPlan pp = pair_sk_plan(M, N, K, pairs);
+    const int64_t pw = (static_cast<int64_t>(pp.num_m) * pp.num_n + pairs - 1) / pairs;
+    const bool pworth = pp.split >= 2 && (1.0 - 1.0 / pp.split) >= 0.10 * static_cast<double>(pw);
+    return pworth ? B200FP8_VARIANT_PAIR256_SPLIT_SK : B200FP8_VARIANT_PAIR256_SPLIT;
+  }
   // A mostly empty last wave is worth splitting along K, but the split-K kernel runs its
   // whole-tile part about 5 % slower (measured) and adds a fix-up pass: only take it when the
   // idle share of the last wave is at least a tenth of the whole run.
@@ -435,7 +466,8 @@ int launch_pair(const void* A, const void* B, const GemmArgs& args, int64_t lda,
   st = make_tmap_u8(&tb, B, args.N, args.K, ldb, SPLIT ? 64 : 128);
   if (st != B200FP8_OK) return st;
   const int64_t tiles = ((args.M + 255) / 256) * ((args.N + 255) / 256);
-  const int pairs = static_cast<int>(tiles < pair_clusters ? tiles : pair_clusters);
+  // (the split-K plan counts on every pair the device can hold)
+  const int pairs = args.sk_split >= 2 ? pair_clusters : static_cast<int>(tiles < pair_clusters ? tiles : pair_clusters);
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -459,7 +491,8 @@ int launch_pair(const void* A, const void* B, const GemmArgs& args, int64_t lda,
       if (st != B200FP8_OK) return st;
     }
     cfg.dynamicSmemBytes = TileCfg<256, true, 128, 1>::SMEM_BYTES;
-    err = cudaLaunchKernelEx(&cfg, gemm_pair_multi_kernel<SPLIT>, ta, tb, args, dm);
+    if (args.sk_split >= 2) err = cudaLaunchKernelEx(&cfg, gemm_pair_multi_sk_kernel, ta, tb, args, dm);   // (SPLIT form only)
+    else err = cudaLaunchKernelEx(&cfg, gemm_pair_multi_kernel<SPLIT>, ta, tb, args, dm);
   } else {
     cfg.dynamicSmemBytes = TileCfg<256, false, 128, 1>::SMEM_BYTES;
     err = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<SPLIT>, ta, tb, args);
@@ -573,19 +606,35 @@ int b200fp8_gemm_pair_clusters(void) {
 }
 
 int b200fp8_gemm_pick_variant(int64_t M, int64_t N, int64_t K) {
-  return pick_variant(M, N, K, sm_count_or_default(), b200fp8_gemm_pair_clusters() > 0);
+  return pick_variant(M, N, K, sm_count_or_default(), b200fp8_gemm_pair_clusters());
 }
 
 int64_t b200fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant) {
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   const int sms = sm_count_or_default();
-  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms, false);   // covers the pair form too (it needs less)
+  if (M == 0 || N == 0 || K == 0) return (variant >= B200FP8_VARIANT_AUTO && variant <= B200FP8_VARIANT_PAIR256_SPLIT_SK) ? 0 : -static_cast<int64_t>(B200FP8_ERR_VARIANT);
+  if (variant == B200FP8_VARIANT_AUTO) {
+    // whatever AUTO may resolve to for this shape, with or without CTA pairs (a destination that cannot
+    // take 16-byte rows falls back to the single-CTA choice)
+    int64_t need = tile_workspace_bytes(M, K);
+    const int v1 = pick_variant(M, N, K, sms, 0);
+    if (v1 == B200FP8_VARIANT_TILE256_SK) need = tile_workspace_bytes(M, K) + tile_sk_plan(M, N, K, sms).partial_bytes;
+    const int pairs = b200fp8_gemm_pair_clusters();
+    if (pairs > 0 && pick_variant(M, N, K, sms, pairs) == B200FP8_VARIANT_PAIR256_SPLIT_SK) {
+      const int64_t np = tile_workspace_bytes(M, K) + pair_sk_plan(M, N, K, pairs).partial_bytes;
+      need = np > need ? np : need;
+    }
+    return need;
+  }
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
     return tile_workspace_bytes(M, K);
   if (variant == B200FP8_VARIANT_TILE256_SK) {
-    if (M == 0 || N == 0 || K == 0) return 0;
     const TileSkPlan p = tile_sk_plan(M, N, K, sms);
+    return p.ast_bytes + p.partial_bytes;
+  }
+  if (variant == B200FP8_VARIANT_PAIR256_SPLIT_SK) {
+    const TileSkPlan p = pair_sk_plan(M, N, K, b200fp8_gemm_pair_clusters());
     return p.ast_bytes + p.partial_bytes;
   }
   if (variant != B200FP8_VARIANT_STREAMK) return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
@@ -619,7 +668,7 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
   const int64_t ldc = dst_ld[0];
   if (M < 0 || N < 0 || K < 0) return B200FP8_ERR_SHAPE;
   if (out_dtype != B200FP8_OUT_BF16 && out_dtype != B200FP8_OUT_FP32) return B200FP8_ERR_DTYPE;
-  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_PAIR256_SPLIT) return B200FP8_ERR_VARIANT;
+  if (variant < B200FP8_VARIANT_AUTO || variant > B200FP8_VARIANT_PAIR256_SPLIT_SK) return B200FP8_ERR_VARIANT;
   if (M == 0 || N == 0) return B200FP8_OK;
   for (int d = 0; d < n_dst; ++d) {
     if (dst[d] == nullptr) return B200FP8_ERR_NULL;
@@ -670,16 +719,21 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
 
   const bool auto_variant = variant == B200FP8_VARIANT_AUTO;
   // (the pair form only pays with the staged output: a destination that cannot take 16-byte rows gets the single-CTA choice)
-  if (auto_variant) variant = pick_variant(M, N, K, dev->sm_count, dev->pair_clusters > 0 && staged && !mc && !fq.rowb);
+  if (auto_variant) variant = pick_variant(M, N, K, dev->sm_count, (staged && !mc && !fq.rowb) ? dev->pair_clusters : 0);
   if (fq.rowb) variant = B200FP8_VARIANT_TILE128;   // the row-scaled promotion exists for the 128-wide tile only
   const bool multi = n_dst > 1 || mc;
   if (fq.rowb && (multi || fused_q)) return B200FP8_ERR_VARIANT;
   // Several destinations (the N-sharded exchange): the pair kernel's smaller pipeline stages leave room
   // for a second set of output staging buffers, which keeps NVLink busy through the next tile's K loop
   if (multi && variant == B200FP8_VARIANT_TILE256_SK) variant = B200FP8_VARIANT_TILE256;
+  // the K ranges of the pair split-K form leave through the fix-up pass, which writes one destination,
+  // and its whole tiles through the staging area
+  if (variant == B200FP8_VARIANT_PAIR256_SPLIT_SK && (multi || !staged || dev->pair_clusters < 1))
+    variant = B200FP8_VARIANT_PAIR256_SPLIT;
   if (auto_variant && n_dst > 1 && !mc && M > 128 && dev->pair_clusters > 0 && variant == B200FP8_VARIANT_TILE256)
     variant = B200FP8_VARIANT_PAIR256_SPLIT;   // (2 GPUs, 8192 x 18432 x 7168: 0.596 vs 0.608 ms for the unsplit form)
-  const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT;
+  const bool pair = variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT ||
+                    variant == B200FP8_VARIANT_PAIR256_SPLIT_SK;
   if (pair && (mc || fq.rowb)) return B200FP8_ERR_VARIANT;
   if (multi && !pair && variant != B200FP8_VARIANT_TILE128 && variant != B200FP8_VARIANT_TILE256)
     return B200FP8_ERR_VARIANT;
@@ -689,10 +743,15 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
     skp = tile_sk_plan(M, N, K, dev->sm_count);
     if (skp.split < 2) variant = B200FP8_VARIANT_TILE256;   // nothing to split: same as the plain tile kernel
   }
+  if (variant == B200FP8_VARIANT_PAIR256_SPLIT_SK) {
+    skp = pair_sk_plan(M, N, K, dev->pair_clusters);
+    if (skp.split < 2) variant = B200FP8_VARIANT_PAIR256_SPLIT;
+  }
 
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_TILE256_SK || pair) {
-    const bool sk = variant == B200FP8_VARIANT_TILE256_SK;
+    const bool pair_sk = variant == B200FP8_VARIANT_PAIR256_SPLIT_SK;
+    const bool sk = variant == B200FP8_VARIANT_TILE256_SK || pair_sk;
     const int64_t prefix = fused_q ? linear_prefix_bytes(M, K) : tile_workspace_bytes(M, K);
     const int64_t need = prefix + (sk ? skp.partial_bytes : 0) + (fq.rowb ? bst_bytes(N, K) : 0);
     if (workspace == nullptr || static_cast<int64_t>(workspace_bytes) < need) return B200FP8_ERR_WORKSPACE;
@@ -753,12 +812,13 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
     const void* a_eff = a_pad ? static_cast<const void*>(a_pad) : A;
     const int64_t lda_eff = a_pad ? align_up(K, 16) : lda;
     if (sk) {
-      st = launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream, skp.grid);
+      st = pair_sk ? launch_pair<true>(a_eff, B, args, lda_eff, ldb, dev->pair_clusters, stream)
+                   : launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream, skp.grid);
       if (st != B200FP8_OK) return st;
-      const dim3 fix_grid(static_cast<unsigned>(skp.tail), 4u);
+      const dim3 fix_grid(static_cast<unsigned>(skp.tail), pair_sk ? 8u : 4u);
       tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, skp.num_kb, ldc,
                                                          out_dtype == B200FP8_OUT_FP32, skp.num_m, skp.num_n,
-                                                         skp.full, skp.split, skp.kb_per);
+                                                         skp.full, skp.split, skp.kb_per, pair_sk ? 1 : 0);
       return launch_status();
     }
     if (variant == B200FP8_VARIANT_PAIR256)
@@ -855,11 +915,22 @@ int64_t b200fp8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int vari
   if (M < 0 || N < 0 || K < 0) return -static_cast<int64_t>(B200FP8_ERR_SHAPE);
   if (M == 0 || N == 0 || K == 0) return 0;
   const int sms = sm_count_or_default();
-  if (variant == B200FP8_VARIANT_AUTO) variant = pick_variant(M, N, K, sms, false);   // covers the pair form too (it needs less)
+  if (variant == B200FP8_VARIANT_AUTO) {
+    int64_t extra = 0;
+    if (pick_variant(M, N, K, sms, 0) == B200FP8_VARIANT_TILE256_SK) extra = tile_sk_plan(M, N, K, sms).partial_bytes;
+    const int pairs = b200fp8_gemm_pair_clusters();
+    if (pairs > 0 && pick_variant(M, N, K, sms, pairs) == B200FP8_VARIANT_PAIR256_SPLIT_SK) {
+      const int64_t ep = pair_sk_plan(M, N, K, pairs).partial_bytes;
+      extra = ep > extra ? ep : extra;
+    }
+    return linear_prefix_bytes(M, K) + extra;
+  }
   if (variant == B200FP8_VARIANT_TILE128 || variant == B200FP8_VARIANT_TILE256 ||
       variant == B200FP8_VARIANT_PAIR256 || variant == B200FP8_VARIANT_PAIR256_SPLIT)
     return linear_prefix_bytes(M, K);
   if (variant == B200FP8_VARIANT_TILE256_SK) return linear_prefix_bytes(M, K) + tile_sk_plan(M, N, K, sms).partial_bytes;
+  if (variant == B200FP8_VARIANT_PAIR256_SPLIT_SK)
+    return linear_prefix_bytes(M, K) + pair_sk_plan(M, N, K, b200fp8_gemm_pair_clusters()).partial_bytes;
   return -static_cast<int64_t>(B200FP8_ERR_VARIANT);
 }
 

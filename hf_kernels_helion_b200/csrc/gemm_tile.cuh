@@ -216,13 +216,13 @@ __device__ __forceinline__ SegCursor seg_begin(int worker, int nworkers) {
 
 // The tail range of this CTA: false if it has none.
 __device__ __forceinline__ bool seg_tail(const GemmArgs& a, int worker, int num_m, int num_n, int num_kb, int num_tiles,
-                                         Segment& s) {
+                                         Segment& s, int group = kRasterGroup) {
   const int u = worker;
   const int tail_tiles = num_tiles - a.sk_full;
   if (u >= tail_tiles * a.sk_split) return false;
   const int t = a.sk_full + u / a.sk_split;
   const int piece = u - (u / a.sk_split) * a.sk_split;
-  tile_coords(t, num_m, num_n, s.m_blk, s.n_blk);
+  tile_coords(t, num_m, num_n, s.m_blk, s.n_blk, group);
   s.kb_begin = piece * a.sk_kb_per;
   s.kb_end = s.kb_begin + a.sk_kb_per < num_kb ? s.kb_begin + a.sk_kb_per : num_kb;
   return s.kb_begin < s.kb_end;
@@ -260,7 +260,7 @@ __device__ __forceinline__ bool seg_next(SegCursor& c, const GemmArgs& a, int nu
   if constexpr (SK == 1) {
     if (!c.tail_done) {
       c.tail_done = true;
-      return seg_tail(a, c.worker, num_m, num_n, num_kb, num_tiles, s);
+      return seg_tail(a, c.worker, num_m, num_n, num_kb, num_tiles, s, c.group);
     }
   }
   return false;
@@ -284,7 +284,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap& tmap_a, const 
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TS = Cfg::TMEM_STAGES;
   constexpr uint32_t H = Cfg::HALVES;
-  static_assert(!(PAIR && (SK || MC || ROWB)), "pair kernels: whole tiles, block scales, plain or TMA-store output");
+  static_assert(!(PAIR && (MC || ROWB)), "pair kernels: block scales, plain or TMA-store output");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -904,6 +904,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   gemm_tile_body<256, false, 0, false, false, 128, SPLIT ? 2 : 1>(tmap_a, tmap_b, args, nullptr);
 }
 
+// The split pair form with the last, partly empty wave of tiles cut into K ranges, one per idle pair
+// (variant pair256_split_sk): whole tiles leave through the staging area as in gemm_pair_multi_kernel,
+// a K range leaves as two fp32 partial tiles (one per CTA) for tile_sk_fixup_kernel.
+__global__ void __launch_bounds__(TileCfg<256, true>::THREADS, 1)
+gemm_pair_multi_sk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const GemmArgs args, const __grid_constant__ DstMaps dmaps) {
+  gemm_tile_body<256, true, 1, false, false, 128, 2>(tmap_a, tmap_b, args, dmaps.m);
+}
+
 template <bool SPLIT>
 __global__ void __launch_bounds__(TileCfg<256, true>::THREADS, 1)
 gemm_pair_multi_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -988,21 +997,25 @@ tile_prep_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t
 // [8 l, 8 l + 8), so that C leaves in whole 512-byte (bf16) or 1-KiB (fp32) row segments.
 __global__ void __launch_bounds__(256)
 tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
-                     int out_fp32, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per) {
+                     int out_fp32, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per, int pair) {
+  // pair != 0: the tiles are 256 rows tall and each K range was left by the two CTAs of a pair, rows
+  // 0..127 in slot 2 u and rows 128..255 in slot 2 u + 1 of range u (grid.y = 8 instead of 4)
   constexpr int BN = 256;
   constexpr int PITCH = BN + 1;                 // floats per staged row: column c of row r sits in bank (r + c) % 32
   __shared__ float stage[32 * PITCH];
   int m_blk, n_blk;
-  tile_coords(sk_full + static_cast<int>(blockIdx.x), num_m, num_n, m_blk, n_blk);
+  tile_coords(sk_full + static_cast<int>(blockIdx.x), num_m, num_n, m_blk, n_blk, pair ? kRasterGroup / 2 : kRasterGroup);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r0 = blockIdx.y * 32;
-  const int64_t row0 = static_cast<int64_t>(m_blk) * 128 + r0;
+  const int rank = static_cast<int>(blockIdx.y) >> 2;
+  const int r0 = (blockIdx.y & 3) * 32;
+  const int64_t row0 = static_cast<int64_t>(m_blk) * (pair ? 256 : 128) + rank * 128 + r0;
   if (row0 >= M) return;
   for (int c4 = warp; c4 < BN / 4; c4 += 8) {
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < sk_split; ++j) {
       if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
-      const int slot = static_cast<int>(blockIdx.x) * sk_split + j;
+      const int unit = static_cast<int>(blockIdx.x) * sk_split + j;
+      const int slot = pair ? 2 * unit + rank : unit;
       if (row0 + lane < M) {
         const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (static_cast<int64_t>(slot) * (BN / 4) + c4) * 128 + r0 + lane);
         sum.x += v.x;

@@ -3,7 +3,7 @@
     python -m hf_kernels_helion_b200.run_case <variant|quant|rowscale> M N K [launches]
 
 `variant` is a name from `_lib.VARIANT_NAMES` ("auto", "tile128", "tile256", "streamk", "tile256_sk", "pair256",
-"pair256_split") and runs `b200fp8_gemm` on random e4m3 operands with scales in [0.5, 1); "rowscale" runs
+"pair256_split", "pair256_split_sk") and runs `b200fp8_gemm` on random e4m3 operands with scales in [0.5, 1); "rowscale" runs
 `b200fp8_gemm_rowscale` (one B scale per row of B); "quant" runs the per-token-group activation quantiser on a
 random bf16 [M, K] matrix (N is ignored). The launches are back to back on one stream, so the
 command is small enough to be wrapped by a profiler capture of a single kernel; the time printed is the mean

@@ -57,6 +57,7 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_TILE256_SK 4 /* 128x256 tiles; the tiles of the last, partly empty wave are split along K over the idle SMs */
 #define B200FP8_VARIANT_PAIR256 5 /* 256x256 tiles on CTA pairs (tcgen05 cta_group::2), each SM holds half of the B tile */
 #define B200FP8_VARIANT_PAIR256_SPLIT 6 /* same, every K block issued and promoted as two 128-column halves */
+#define B200FP8_VARIANT_PAIR256_SPLIT_SK 7 /* same as 6, the pair tiles of the last, partly empty wave split along K over the idle pairs */
 
 /* codes a kernel may leave in *status_word */
 #define B200FP8_DEV_OK 0u

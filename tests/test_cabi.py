@@ -116,7 +116,7 @@ def test_workspace_and_variant_queries(lib):
     # (K-block-major scales + the 16-row copy of A that M <= 16 goes through)
     assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, TSK) == 64 * 128 * 4 + 16 * 8192
     assert lib.b200fp8_gemm_workspace_bytes(17, 28672, 8192, TSK) == 64 * 128 * 4
-    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256, 4, 5, 6)   # 5, 6 (CTA pairs) where the device can run clusters of two
+    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) in (T128, T256, 4, 5, 6, 7)   # 5 to 7: CTA pairs where the device can run clusters of two
 
 
 @pytest.mark.parametrize("tiles,num_kb,grid", [(224, 64, 148), (8, 8, 148), (3, 5, 4), (1, 1, 1), (7, 3, 5),

@@ -25,7 +25,7 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 FP32_TOL = 1e-4
-VARIANTS_BIG = ["tile128", "tile256", "pair256", "pair256_split"]
+VARIANTS_BIG = ["tile128", "tile256", "pair256", "pair256_split", "pair256_split_sk"]
 
 
 def _dev(ts, device):
@@ -38,7 +38,8 @@ def _run(device, A, B, As, Bs, dtype, variant):
     return out.cpu()
 
 
-@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk", "pair256", "pair256_split", "auto"])
+@pytest.mark.parametrize("variant", ["tile128", "tile256", "streamk", "tile256_sk", "pair256", "pair256_split",
+                                     "pair256_split_sk", "auto"])
 @pytest.mark.parametrize("name", ["small_96x256x384", "small_130x128x256", "small_1x384x512"])
 def test_golden_vectors_from_reference_source(device, name, variant):
     z = np.load(GOLDEN / f"{name}.npz")
@@ -251,6 +252,29 @@ def test_torch_compile_traces_the_op(device):
     assert torch.equal(f(A, B, As, Bs), eager)
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 1280, 2048), (512, 12032, 1024), (1000, 1304, 1152), (300, 2560, 4096)])
+def test_pair_tail_split_k(device, M, N, K):
+    """pair256_split_sk on shapes whose last wave of 256 x 256 pair tiles really is cut into K ranges
+    (10 tiles x 4 ranges; 74 whole tiles + 20 x 2 ranges; ragged M, N and K; rows 256..299 only in the
+    second CTA): the sum of the ranges must match the oracle like any other variant, and the whole
+    tiles must carry the bits of the unsplit kernel."""
+    A, B, As, Bs = oracle.make_quantised_inputs(M, N, K, M + N + K)
+    dA, dB, dAs, dBs = _dev((A, B, As, Bs), device)
+    ref = oracle.gemm_dequant(A, B, As, Bs)
+    for dtype in (torch.float32, torch.bfloat16):
+        out = runtime.gemm(dA, dB, dAs, dBs, 128, 128, dtype, variant="pair256_split_sk")
+        runtime.check_device_status()
+        if dtype == torch.float32:
+            assert oracle.max_err_over_rms(out.cpu(), ref) <= FP32_TOL
+            plain = runtime.gemm(dA, dB, dAs, dBs, 128, 128, dtype, variant="pair256_split")
+            assert oracle.max_err_over_rms(out.cpu(), plain.cpu()) <= 2e-6
+        else:
+            assert oracle.bf16_ulp_error(out.cpu(), ref) <= 1
+    # twice the same bits: the ranges are added in a fixed order
+    again = runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="pair256_split_sk")
+    assert torch.equal(again, runtime.gemm(dA, dB, dAs, dBs, 128, 128, torch.float32, variant="pair256_split_sk"))
+
+
 def test_auto_takes_cta_pairs_where_they_pay(device):
     """AUTO = 256 x 256 tiles on CTA pairs for M > 256 with an even number of 128-row blocks, when the
     destination takes 16-byte rows (the output is then staged and stored by TMA); otherwise the
@@ -259,7 +283,7 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     pair = _lib.VARIANT_NAMES["pair256_split"]
     assert lib.b200fp8_gemm_pair_clusters() > 0
     assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == pair
-    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == pair
+    assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == _lib.VARIANT_NAMES["pair256_split_sk"]   # 34 tiles in the last wave of 74
     assert lib.b200fp8_gemm_pick_variant(640, 4096, 1024) != pair      # five row blocks
     assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == pair
     assert lib.b200fp8_gemm_pick_variant(128, 28672, 8192) == _lib.VARIANT_TILE256
@@ -273,7 +297,7 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     runtime.check_device_status()
 
 
-@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk", "pair256", "pair256_split"])
+@pytest.mark.parametrize("variant", ["auto", "tile128", "tile256", "tile256_sk", "pair256", "pair256_split", "pair256_split_sk"])
 @pytest.mark.parametrize("M,N,K", [(1, 384, 512), (5, 256, 1024), (16, 1280, 2048), (130, 384, 256), (640, 4096, 1024),
                                    (512, 1024, 1024)])   # the last one: an even number of row blocks, AUTO = CTA pairs
 def test_fused_quantise_and_multiply_equals_the_two_calls(device, M, N, K, variant):
