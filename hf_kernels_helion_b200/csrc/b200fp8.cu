@@ -815,10 +815,21 @@ static int gemm_impl(bool mc, const void* A, const void* B, const float* As, con
       st = pair_sk ? launch_pair<true>(a_eff, B, args, lda_eff, ldb, dev->pair_clusters, stream)
                    : launch_tile<256>(a_eff, B, args, lda_eff, ldb, dev->sm_count, stream, skp.grid);
       if (st != B200FP8_OK) return st;
-      const dim3 fix_grid(static_cast<unsigned>(skp.tail), pair_sk ? 8u : 4u);
-      tile_sk_fixup_kernel<<<fix_grid, 256, 0, stream>>>(args.partial, C, M, N, skp.num_kb, ldc,
-                                                         out_dtype == B200FP8_OUT_FP32, skp.num_m, skp.num_n,
-                                                         skp.full, skp.split, skp.kb_per, pair_sk ? 1 : 0);
+      cudaLaunchAttribute fattr[1];
+      fattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      fattr[0].val.programmaticStreamSerializationAllowed = 1;
+      cudaLaunchConfig_t fcfg = {};
+      fcfg.gridDim = dim3(static_cast<unsigned>(skp.tail), pair_sk ? 8u : 4u, 4u);
+      fcfg.blockDim = dim3(256);
+      fcfg.stream = stream;
+      fcfg.attrs = fattr;
+      fcfg.numAttrs = 1;
+      if (cudaLaunchKernelEx(&fcfg, tile_sk_fixup_kernel, static_cast<const float*>(args.partial), C, M, N, skp.num_kb,
+                             ldc, static_cast<int>(out_dtype == B200FP8_OUT_FP32), skp.num_m, skp.num_n, skp.full,
+                             skp.split, skp.kb_per, pair_sk ? 1 : 0) != cudaSuccess) {
+        cudaGetLastError();
+        return B200FP8_ERR_LAUNCH;
+      }
       return launch_status();
     }
     if (variant == B200FP8_VARIANT_PAIR256)

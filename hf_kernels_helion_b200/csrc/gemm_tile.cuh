@@ -994,80 +994,78 @@ tile_prep_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t
 }
 
 // Tail split-K: adds the K ranges of every tail tile (ascending range order: fixed, hence
-// bit-reproducible) and writes C. Grid = (tail tiles, 4 chunks of 32 rows); 256 threads.
-// Phase 1: warp w sums the float4 column groups w, w + 8, ... of the chunk's 32 rows (lane = row:
-// 512 contiguous bytes per load in the partial-tile layout of sk_partial_ptr) and parks the sums
-// in shared memory; phase 2: warp w writes rows w, w + 8, ... with lane l holding columns
-// [8 l, 8 l + 8), so that C leaves in whole 512-byte (bf16) or 1-KiB (fp32) row segments.
+// bit-reproducible) and writes C. Grid = (tail tiles, chunks of 32 rows: 4, or 8 for pair tiles,
+// 4 quarters of 64 columns); 256 threads. Phase 1: warp w sums the float4 column groups 2 w and
+// 2 w + 1 of the quarter for the chunk's 32 rows (lane = row: 512 contiguous bytes per load in the
+// partial-tile layout of sk_partial_ptr; the loads of all ranges are independent and go out
+// together) and parks the sums in shared memory; phase 2: warp w writes rows w, w + 8, ... with
+// lane l holding columns 2 l, 2 l + 1, so that C leaves in whole 128-byte (bf16) or 256-byte
+// (fp32) row segments. Launched with programmatic stream serialisation: it may be scheduled
+// while the GEMM drains, and waits for it here before it reads.
 __global__ void __launch_bounds__(256)
 tile_sk_fixup_kernel(const float* __restrict__ partial, void* C, int64_t M, int64_t N, int num_kb, int64_t ldc,
                      int out_fp32, int num_m, int num_n, int sk_full, int sk_split, int sk_kb_per, int pair) {
   // pair != 0: the tiles are 256 rows tall and each K range was left by the two CTAs of a pair, rows
   // 0..127 in slot 2 u and rows 128..255 in slot 2 u + 1 of range u (grid.y = 8 instead of 4)
   constexpr int BN = 256;
-  constexpr int PITCH = BN + 1;                 // floats per staged row: column c of row r sits in bank (r + c) % 32
+  constexpr int QN = 64;                        // columns per CTA
+  constexpr int PITCH = QN + 1;                 // floats per staged row: column c of row r sits in bank (r + c) % 32
   __shared__ float stage[32 * PITCH];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   int m_blk, n_blk;
   tile_coords(sk_full + static_cast<int>(blockIdx.x), num_m, num_n, m_blk, n_blk, pair ? kRasterGroup / 2 : kRasterGroup);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(blockIdx.y) >> 2;
   const int r0 = (blockIdx.y & 3) * 32;
+  const int cq = static_cast<int>(blockIdx.z);   // column quarter
   const int64_t row0 = static_cast<int64_t>(m_blk) * (pair ? 256 : 128) + rank * 128 + r0;
   if (row0 >= M) return;
-  for (int c4 = warp; c4 < BN / 4; c4 += 8) {
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 sum[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  if (row0 + lane < M) {
     for (int j = 0; j < sk_split; ++j) {
       if (j * sk_kb_per >= num_kb) break;   // empty range: nothing was written
       const int unit = static_cast<int>(blockIdx.x) * sk_split + j;
       const int slot = pair ? 2 * unit + rank : unit;
-      if (row0 + lane < M) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c4 = cq * (QN / 4) + 2 * warp + i;
         const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (static_cast<int64_t>(slot) * (BN / 4) + c4) * 128 + r0 + lane);
-        sum.x += v.x;
-        sum.y += v.y;
-        sum.z += v.z;
-        sum.w += v.w;
+        sum[i].x += v.x;
+        sum[i].y += v.y;
+        sum[i].z += v.z;
+        sum[i].w += v.w;
       }
     }
-    float* dst = stage + lane * PITCH + c4 * 4;
-    dst[0] = sum.x;
-    dst[1] = sum.y;
-    dst[2] = sum.z;
-    dst[3] = sum.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float* dst = stage + lane * PITCH + (2 * warp + i) * 4;
+    dst[0] = sum[i].x;
+    dst[1] = sum[i].y;
+    dst[2] = sum[i].z;
+    dst[3] = sum[i].w;
   }
   __syncthreads();
-  const int64_t col0 = static_cast<int64_t>(n_blk) * BN + lane * 8;
+  const int64_t col0 = static_cast<int64_t>(n_blk) * BN + cq * QN + lane * 2;
   for (int r = warp; r < 32; r += 8) {
     const int64_t row = row0 + r;
     if (row >= M) break;
-    const float* src = stage + r * PITCH + lane * 8;
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = src[j];
+    const float v0 = stage[r * PITCH + lane * 2], v1 = stage[r * PITCH + lane * 2 + 1];
     if (out_fp32) {
       float* crow = reinterpret_cast<float*>(C) + row * ldc + col0;
-      if (col0 + 8 <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
-        *reinterpret_cast<float4*>(crow) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(crow + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      if (col0 + 2 <= N && (reinterpret_cast<uintptr_t>(crow) & 7u) == 0) {
+        *reinterpret_cast<float2*>(crow) = make_float2(v0, v1);
       } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (col0 + j < N) crow[j] = v[j];
+        if (col0 < N) crow[0] = v0;
+        if (col0 + 1 < N) crow[1] = v1;
       }
     } else {
       __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + row * ldc + col0;
-      if (col0 + 8 <= N && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
-        uint4 u;
-        u.x = *reinterpret_cast<uint32_t*>(&p0);
-        u.y = *reinterpret_cast<uint32_t*>(&p1);
-        u.z = *reinterpret_cast<uint32_t*>(&p2);
-        u.w = *reinterpret_cast<uint32_t*>(&p3);
-        *reinterpret_cast<uint4*>(crow) = u;
+      if (col0 + 2 <= N && (reinterpret_cast<uintptr_t>(crow) & 3u) == 0) {
+        *reinterpret_cast<__nv_bfloat162*>(crow) = __floats2bfloat162_rn(v0, v1);
       } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (col0 + j < N) crow[j] = __float2bfloat16_rn(v[j]);
+        if (col0 < N) crow[0] = __float2bfloat16_rn(v0);
+        if (col0 + 1 < N) crow[1] = __float2bfloat16_rn(v1);
       }
     }
   }
