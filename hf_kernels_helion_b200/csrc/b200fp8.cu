@@ -363,10 +363,12 @@ int pick_variant(int64_t M, int64_t N, int64_t K, int sm_count, int pairs) {
   // With the stores out of the way the form that issues each K block as two 128-column halves is the
   // faster of the two pair kernels (same shapes: 1.002 vs 1.016 ms, 1846 vs 1811 sustained; 136.2 vs 139.4 us).
   if (pair_ok && num_m % 2 == 0) {
-    // a mostly empty last wave of pair tiles is split along K under the same rule as below
+    // a partly empty last wave of pair tiles is split along K. The pair form's whole-tile part is not slower
+    // for it and the fix-up pass is a few microseconds, so the bar is low: the idle share of the last wave
+    // at least a fiftieth of the run (8192 x 18432 x 7168, 10 tiles in the 32nd wave: 986-989 vs 999-1000 us)
     const TileSkPlan pp = pair_sk_plan(M, N, K, pairs);
     const int64_t pw = (static_cast<int64_t>(pp.num_m) * pp.num_n + pairs - 1) / pairs;
-    const bool pworth = pp.split >= 2 && (1.0 - 1.0 / pp.split) >= 0.10 * static_cast<double>(pw);
+    const bool pworth = pp.split >= 2 && (1.0 - 1.0 / pp.split) >= 0.02 * static_cast<double>(pw);
     return pworth ? B200FP8_VARIANT_PAIR256_SPLIT_SK : B200FP8_VARIANT_PAIR256_SPLIT;
   }
   // A mostly empty last wave is worth splitting along K, but the split-K kernel runs its

@@ -282,7 +282,8 @@ def test_auto_takes_cta_pairs_where_they_pay(device):
     lib = _lib.load()
     pair = _lib.VARIANT_NAMES["pair256_split"]
     assert lib.b200fp8_gemm_pair_clusters() > 0
-    assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == pair
+    assert lib.b200fp8_gemm_pick_variant(8192, 18432, 7168) == _lib.VARIANT_NAMES["pair256_split_sk"]   # 10 tiles in the 32nd wave
+    assert lib.b200fp8_gemm_pick_variant(2048, 2048, 4096) == pair                                     # 64 tiles: one wave, nothing to split
     assert lib.b200fp8_gemm_pick_variant(4096, 4096, 8192) == _lib.VARIANT_NAMES["pair256_split_sk"]   # 34 tiles in the last wave of 74
     assert lib.b200fp8_gemm_pick_variant(640, 4096, 1024) != pair      # five row blocks
     assert lib.b200fp8_gemm_pick_variant(256, 28672, 8192) == pair
