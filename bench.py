@@ -622,7 +622,7 @@ def main_ours(args):
         # DRAM bytes of one GEMM launch at 1 GPU, from one profiler capture of this kernel on this shape
         # (dram__bytes_read.sum / dram__bytes_write.sum); at N > 1 scaled by the share of the weight and of
         # the output a rank touches (A is read whole by every rank). Not re-measured by this run.
-        traffic_1gpu = {"read": 530.2e6, "write": 288.1e6}
+        traffic_1gpu = {"read": 482.3e6, "write": 295.5e6}
         traffic = (M * K + (traffic_1gpu["read"] - M * K) / world) + traffic_1gpu["write"] / world
         if world == 1:
             step_desc = "fp8_act_quant(A bf16) + w8a8_block_fp8_matmul"
