@@ -98,6 +98,12 @@ def test_workspace_and_variant_queries(lib):
     # 512 tiles on 148 SMs: 444 whole tiles + 68 tail tiles cut into 2 K ranges each (fp32 partial tiles)
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 4) == ast + 68 * 2 * 128 * 256 * 4
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, AUTO) in (ast, ast + 68 * 2 * 128 * 256 * 4)
+    # CTA-pair forms: the plain ones need the scale copy only; the split-K one adds two partial tiles per K range
+    # (34 tail tiles x 2 ranges x 2 CTAs on a device with 74 pairs; nothing where the device reports no pairs)
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 5) == ast
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 6) == ast
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 7) in (ast, ast + 34 * 2 * 2 * 128 * 256 * 4)
+    assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, 8) == -5
     assert lib.b200fp8_gemm_workspace_bytes(300, 512, 200, T128) == 2 * 384 * 4   # M padded to 128, K blocks rounded up
     assert lib.b200fp8_gemm_workspace_bytes(4096, 4096, 8192, SK) == -5     # M > 256 cannot use stream-K
     assert lib.b200fp8_gemm_workspace_bytes(16, 28672, 8192, 42) == -5
